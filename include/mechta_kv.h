@@ -1,0 +1,198 @@
+/* mechta_kv.h — C ABI of the B200 KV-cache / attention path that stands in for the KV operators of
+ * ssomenzi/mechta (reference paths below: M/ = engine/crates/mechta/src/, W/ = M/wgsl/).
+ *
+ * The reference has no FFI for this path: its boundary is a fixed set of compute dispatches over named
+ * buffers with an 8-word uniform P{n, rows, f0, f1, step_a, step_o, flag, extra} (W/ops.wgsl:4). Each entry
+ * point below replaces one group of those dispatches and says which. A Rust `-sys` crate binds exactly
+ * these symbols; mkv_dispatch() additionally accepts the reference's own (kernel name, uniform) form.
+ *
+ * Conventions
+ *  - Every call returns an mkv_status; nothing aborts. mkv_last_error() gives the text of the last failure
+ *    on the calling thread.
+ *  - One mkv_ctx = one CUDA device + one compute stream (+ one copy stream). Calls on a ctx come from one
+ *    host thread at a time (the reference engine is single-threaded, engine/crates/api/src/lib.rs:46) and are
+ *    stream-ordered: they return once the work is enqueued, except where "blocks" is written.
+ *  - Pointers named *_dev are device pointers on the ctx's device, borrowed for the call; *_host are host
+ *    pointers (pinned memory makes the copies asynchronous).
+ *  - Shapes are the reference's: 16 query heads, 2 KV heads, head_dim 256, scale 1/16; one cache position is
+ *    512 elements of K and 512 of V, element (pos, kvh, d) at pos*512 + kvh*256 + d (W/ops.wgsl:165).
+ *  - Positions are global token positions. A cache may hold only a contiguous shard [shard_first,
+ *    shard_first + capacity) of the sequence (sequence sharding over several GPUs, one process each).
+ *  - There is no CPU fallback: without a usable CUDA device every compute call fails with MKV_ERR_CUDA.
+ */
+#ifndef MECHTA_KV_H
+#define MECHTA_KV_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct mkv_ctx mkv_ctx;
+typedef struct mkv_cache mkv_cache;
+
+typedef enum {
+    MKV_OK = 0,
+    MKV_ERR_INVALID = 1,     /* bad argument (null, ntok out of range, misaligned pointer, unknown op) */
+    MKV_ERR_CAPACITY = 2,    /* position range outside the cache (the reference asserts pos + K < ctx, M/quad.rs:278) */
+    MKV_ERR_CUDA = 3,        /* a CUDA call failed or no device */
+    MKV_ERR_NOMEM = 4,       /* device or host allocation failed */
+    MKV_ERR_UNSUPPORTED = 5, /* valid in the reference but not built here */
+    MKV_ERR_STATE = 6,       /* reads rows that were never appended or were rolled back */
+    MKV_ERR_FORMAT = 7,      /* snapshot / root file does not match the cache */
+    MKV_ERR_IO = 8           /* file system error (root files) */
+} mkv_status;
+
+/* M/engine.rs:49-68 KvFormat */
+typedef enum { MKV_F16 = 0, MKV_F32 = 1 } mkv_fmt;
+
+enum {
+    MKV_HQ = 16, MKV_HKV = 2, MKV_D = 256, MKV_GROUP = 8, MKV_ROW = 512,
+    MKV_MAX_VERIFY = 4,      /* K of M/quad.rs: tokens per verify step */
+    MKV_REC = 258,           /* one partial record [m, l, acc[256]] (W/ops.wgsl:389-391, M/dmx.rs:111) */
+    MKV_CTX_MIN = 4096, MKV_CTX_MAX = 262144 /* M/engine.rs:24-25 */
+};
+
+const char *mkv_strerror(mkv_status s);
+const char *mkv_last_error(void);
+/* "mechta-kv <version> sm_100a" */
+const char *mkv_version(void);
+
+/* ---- context ------------------------------------------------------------------------------------------
+ * Replaces gpu::Gpu's device/queue for this path (engine/crates/gpu/src/lib.rs:60-139). `stream` is a
+ * cudaStream_t to run on (borrowed; e.g. the caller's current stream) or NULL for a stream the ctx creates. */
+mkv_status mkv_ctx_create(int device, void *stream, mkv_ctx **out);
+void mkv_ctx_destroy(mkv_ctx *ctx);
+/* blocks until everything enqueued on both streams has finished */
+mkv_status mkv_sync(mkv_ctx *ctx);
+/* number of this library's kernels launched on the ctx since creation (for launch accounting) */
+uint64_t mkv_launch_count(const mkv_ctx *ctx);
+/* Kernel timing with CUDA events on the compute stream, off by default. While on, every attention core
+ * kernel (verify / prefill) is bracketed by two events; mkv_prof_read blocks on the last one and returns
+ * the summed milliseconds and the number of launches since the last read, then clears them. Mirrors the
+ * reference's per-dispatch GPU timestamps of "attn.core" (M/engine.rs:1274-1295). */
+mkv_status mkv_prof_enable(mkv_ctx *ctx, int on);
+mkv_status mkv_prof_read(mkv_ctx *ctx, double *core_ms, uint64_t *core_launches);
+
+/* ---- cache --------------------------------------------------------------------------------------------
+ * Replaces the per-layer buffers kc[il], vc[il] (M/engine.rs:493-494,602-603): n_layers x (K, V), each
+ * [capacity][2][256] of f16 or f32, zero-filled (wgpu zero-initialises; the tail tile of the attention
+ * reads rows past the valid length and masks them, M/dmx.rs:53,60-64).
+ * capacity_tokens: rows held here. For an unsharded cache (shard_first = 0) it must satisfy the reference's
+ * rule: a multiple of 1024 in [4096, 262144] (M/engine.rs:28-33). A shard may be any multiple of 64. */
+mkv_status mkv_cache_create(mkv_ctx *ctx, mkv_fmt fmt, int n_layers, uint32_t capacity_tokens,
+                            uint32_t shard_first, mkv_cache **out);
+void mkv_cache_destroy(mkv_cache *c);
+/* device pointers of a layer's K and V buffers (for tests and for hosts that fill the cache themselves) */
+mkv_status mkv_cache_buffers(mkv_cache *c, int layer, void **k_dev, void **v_dev);
+/* rows currently valid: the global position after the last appended row (0 when empty) */
+uint32_t mkv_cache_len(const mkv_cache *c);
+/* declare rows [.., len) valid without appending (after the host filled the buffers itself, or restore) */
+mkv_status mkv_cache_set_len(mkv_cache *c, uint32_t len);
+/* M/memcheck.rs:14-20 need_bytes minus its fixed part: K and V of n_layers + the reference's partials */
+uint64_t mkv_need_bytes(uint32_t ctx_tokens, mkv_fmt fmt, int n_layers);
+/* bytes this library allocates on the device for such a cache (buffers + its own split-K scratch) */
+uint64_t mkv_cache_device_bytes(const mkv_cache *c);
+
+/* ---- append: replaces kv_rope2 / kv_rope + kv_copy (W/kv.wgsl:19-42) and rope2 / rope + copy
+ * (W/ops.wgsl:141-162,275-286), dispatched at M/quad.rs:116-117, M/engine.rs:1213-1214.
+ * k_dev = `kn` f32 [ntok][2][256] (after the K RMSNorm), v_dev = `vb` f32 [ntok][512],
+ * rope_tab_dev = f32 [ntok][64] = [cos 0..31 | sin 0..31] per token (mkv_rope_table), or NULL when K is
+ * already rotated. Token t goes to global position pos + t; rows outside this cache's shard are skipped.
+ * Afterwards the valid length is pos + ntok (rows beyond it, e.g. refused drafts, are forgotten).
+ * Products and the sum/difference of the rotation are rounded separately (no FMA); f16 stores round to
+ * nearest even. 1 <= ntok <= 4096. */
+mkv_status mkv_append(mkv_cache *c, int layer, uint32_t pos, uint32_t ntok, const float *k_dev,
+                      const float *v_dev, const float *rope_tab_dev);
+/* the same for every layer in one launch: k_dev/v_dev/rope as above with a leading [n_layers] axis on
+ * k and v (the table is shared by the layers) */
+mkv_status mkv_append_layers(mkv_cache *c, uint32_t pos, uint32_t ntok, const float *k_dev,
+                             const float *v_dev, const float *rope_tab_dev);
+/* M/engine.rs:108-114 rope_table, on the host: out[ntok][64] for positions pos..pos+ntok-1 */
+void mkv_rope_table(int32_t pos, uint32_t ntok, float *out_host);
+
+/* ---- rollback: the reference has no kernel for it; the session simply continues at a smaller pos
+ * (M/session.rs:385-411, M/engine.rs:703-705). new_len <= current length. Rows >= new_len stay in memory
+ * until overwritten and are never visible to later reads. scrub != 0 also zeroes them (deterministic
+ * snapshots of the whole buffer). */
+mkv_status mkv_truncate(mkv_cache *c, uint32_t new_len, int scrub);
+
+/* ---- decode / verify attention: replaces q_dmx + attn_dmx1/attn_dmx2 + attn_fd_combine (M/dmx.rs:19-141,
+ * M/quad.rs:122-124) for the f16 cache, and attn_fd / attn_fd2h + attn_fd_combine (W/ops.wgsl:325-538,
+ * M/quad.rs:129-130, M/engine.rs:133-142) for the f32 cache and the MTP window.
+ * q_dev = `qr` f32 [ntok][16][256] after RoPE; out_dev = `att` f32 [ntok][16][256]. Token t (at pos + t) sees
+ * keys first_pos <= key < pos + 1 + t, which includes the rows this step appended. 1 <= ntok <= 4.
+ * Requires pos + ntok <= valid length and an unsharded cache. */
+mkv_status mkv_attn_verify(mkv_cache *c, int layer, uint32_t first_pos, uint32_t pos, uint32_t ntok,
+                           const float *q_dev, float *out_dev);
+
+/* Sequence-sharded form. Each shard computes, over the keys it holds, the un-normalised record
+ * rec_dev = f32 [64][258], row = tok*16 + head, [M, tot, acc[256]] — the reference's partial format
+ * (W/ops.wgsl:389-391) with one record per row; rows that see no key here get M = -3e38, tot = 0.
+ * Records of all shards are gathered by the host (NCCL all-gather) and merged by mkv_combine_shards,
+ * which is attn_fd_combine's arithmetic (W/ops.wgsl:529-537) over shards instead of blocks. */
+mkv_status mkv_attn_verify_partial(mkv_cache *c, int layer, uint32_t first_pos, uint32_t pos, uint32_t ntok,
+                                   const float *q_dev, float *rec_dev);
+mkv_status mkv_combine_shards(mkv_ctx *ctx, const float *recs_dev /*[n_shards][64][258]*/, int n_shards,
+                              uint32_t ntok, float *out_dev /*[ntok][16][256]*/);
+
+/* Ragged batch: n independent (cache, layer, position) verify steps in one launch pair; every cache must
+ * belong to `ctx`. Each item behaves exactly as one mkv_attn_verify call. */
+typedef struct {
+    mkv_cache *cache;
+    int32_t layer;
+    uint32_t first_pos, pos, ntok;
+    const float *q_dev; /* [ntok][16][256] */
+    float *out_dev;     /* [ntok][16][256] */
+} mkv_verify_item;
+mkv_status mkv_attn_verify_batch(mkv_ctx *ctx, const mkv_verify_item *items, int n);
+
+/* ---- prefill attention over the cache: replaces q_f16 + attn_fa_mx + attn_fd_combine (W/fa_mx.wgsl:19-115,
+ * 313-319), attn_fa and attn_fd4 (W/ops.wgsl:562-651,711-778), dispatched at M/engine.rs:1215-1241.
+ * The block's K/V must already be appended (the reference appends all rows first, M/engine.rs:1213-1214).
+ * q_dev f32 [ntok][16][256]; token T sees keys first_pos <= key < pos0 + 1 + T; out f32 [ntok][16][256]. */
+mkv_status mkv_attn_prefill(mkv_cache *c, int layer, uint32_t first_pos, uint32_t pos0, uint32_t ntok,
+                            const float *q_dev, float *out_dev);
+
+/* ---- snapshot / restore of the prefix cache ("root"): replaces the KV part of Engine::read_root /
+ * write_root (M/engine.rs:782-823). Payload = for each layer in order, K rows [0,p) then V rows [0,p), raw
+ * cache bytes (f16 bit patterns or f32), i.e. Root.kv flattened. A shard copies only the rows it holds; its
+ * payload then covers [max(0,shard_first), min(p, shard_first+capacity)).
+ * The copies run on the ctx's copy stream after the work already enqueued on the compute stream; with pinned
+ * host memory the call returns at once. Compute enqueued later waits for a restore; mkv_snapshot_wait blocks
+ * until the last snapshot has landed in host memory. */
+size_t mkv_snapshot_bytes(const mkv_cache *c, uint32_t p);
+mkv_status mkv_snapshot(mkv_cache *c, uint32_t p, void *dst_host, size_t cap, size_t *written);
+mkv_status mkv_snapshot_wait(mkv_cache *c);
+/* afterwards the valid length is p (on a shard: min(p, end of shard)) */
+mkv_status mkv_restore(mkv_cache *c, uint32_t p, const void *src_host, size_t bytes);
+/* pinned host staging, so hosts without their own CUDA binding get asynchronous copies */
+mkv_status mkv_host_alloc(size_t bytes, void **out);
+void mkv_host_free(void *p);
+
+/* ---- root files: the KV section of the reference's on-disk prefix cache, "MECHTA-ROOT-1\n"
+ * (M/session.rs:92-129): u64 p, u64 n_ssm, u64 n_kv, p x u32 tokens, then length-prefixed f32-word vectors
+ * ssm.., conv.., (K, V)... Files written here carry n_ssm = 0; files with DeltaNet states are read and the
+ * states skipped. payload = mkv_snapshot's layout. Blocks (host I/O only). */
+mkv_status mkv_root_write(const char *path, mkv_fmt fmt, int n_layers, uint32_t p, const uint32_t *tokens,
+                          const void *payload_host, size_t payload_bytes);
+mkv_status mkv_root_read(const char *path, mkv_fmt fmt, int n_layers, uint32_t *p_out, uint32_t *tokens_out,
+                         size_t tokens_cap, void *payload_host, size_t payload_cap, size_t *payload_bytes);
+/* M/session.rs:61-66 root_key: FNV-1a 64 of the token ids */
+uint64_t mkv_root_key(const uint32_t *tokens, size_t n);
+
+/* ---- the reference's own dispatch form ------------------------------------------------------------------
+ * op = the WGSL entry point name, u = its 8-word uniform, in0/in1 = bindings 0 and 1 (device), out = the
+ * output binding (device; ignored by the cache writers). Supported: "kv_rope", "kv_rope2", "rope", "rope2"
+ * (K writers: in0 = kn, in1 = table, u = [256, rows, 0,0, 256,256, flag, pos*512]), "kv_copy", "copy"
+ * (V writer: in0 = vb, u = [n, .., extra = pos*512]), "attn_dmx1", "attn_dmx2", "attn_fd", "attn_fd2h"
+ * (in0 = qr f32; u as M/quad.rs:286 / M/engine.rs:629; runs the core AND the combine, out = att),
+ * "attn_fd_combine", "q_dmx" (no-ops: fused into the attention entry). Anything else: MKV_ERR_UNSUPPORTED. */
+mkv_status mkv_dispatch(mkv_cache *c, int layer, const char *op, const uint32_t u[8], const void *in0,
+                        const void *in1, void *out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,910 @@
+// C-ABI host side of libmechta_kv: contexts, caches, argument checks, stream ordering. The kernels are in the
+// other .cu files; the declarations and their reference citations are in include/mechta_kv.h.
+#include <math.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <algorithm>
+#include <new>
+
+#include "internal.cuh"
+
+namespace mkv {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof g_err, fmt, ap);
+    va_end(ap);
+}
+
+mkv_status prefill_setup_device();
+mkv_status launch_prefill_f16_mma(Ctx *ctx, Cache *c, int layer, uint32_t first_pos, uint32_t pos0, uint32_t ntok,
+                                  const float *q, float *out);
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// Tensor map of one K or V buffer seen as [rows][512] elements; boxes of 128 bytes x `box_rows` rows with the
+// 128-byte swizzle. Rows past the end read as zero.
+static mkv_status make_tensor_map(CUtensorMap *out, mkv_fmt fmt, void *base, uint32_t rows, uint32_t box_rows) {
+    EncodeTiledFn enc = encode_tiled();
+    if (!enc) {
+        set_error("cuTensorMapEncodeTiled is not available from the driver");
+        return MKV_ERR_CUDA;
+    }
+    const size_t elem = fmt == MKV_F16 ? 2 : 4;
+    cuuint64_t dims[2] = {512, rows};
+    cuuint64_t strides[1] = {512 * elem};
+    cuuint32_t box[2] = {(cuuint32_t)(128 / elem), box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(out, fmt == MKV_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, base, dims,
+                     strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled failed with %d", (int)r);
+        return MKV_ERR_CUDA;
+    }
+    return MKV_OK;
+}
+
+static mkv_status use_device(Ctx *ctx) {
+    MKV_CUDA(cudaSetDevice(ctx->device));
+    return MKV_OK;
+}
+
+// Reads and clears the device status word (blocks); nonzero means a kernel gave up on a wait.
+static mkv_status check_device_status(Ctx *ctx) {
+    uint32_t st = 0;
+    MKV_CUDA(cudaMemcpy(&st, ctx->dev_status, 4, cudaMemcpyDeviceToHost));
+    if (st != 0) {
+        MKV_CUDA(cudaMemset(ctx->dev_status, 0, 4));
+        set_error("a kernel reported status 0x%x (1 = a bounded wait ran out)", st);
+        return MKV_ERR_CUDA;
+    }
+    return MKV_OK;
+}
+
+static mkv_status ensure_scratch(Cache *c, size_t pieces) {
+    if (pieces <= c->scratch_pieces) return MKV_OK;
+    Ctx *ctx = c->ctx;
+    // earlier launches may still read the old buffers
+    MKV_CUDA(cudaStreamSynchronize(ctx->stream));
+    if (c->part_ml) cudaFree(c->part_ml);
+    if (c->part_o) cudaFree(c->part_o);
+    c->part_ml = c->part_o = nullptr;
+    c->scratch_pieces = 0;
+    if (cudaMalloc(&c->part_ml, pieces * 32 * 2 * sizeof(float)) != cudaSuccess ||
+        cudaMalloc(&c->part_o, pieces * 32 * 256 * sizeof(float)) != cudaSuccess) {
+        cudaGetLastError();
+        set_error("out of device memory for %zu split-K pieces", pieces);
+        return MKV_ERR_NOMEM;
+    }
+    c->scratch_pieces = pieces;
+    return MKV_OK;
+}
+
+// Fills the position-dependent part of an item and its tile range. Returns MKV_ERR_* on bad arguments.
+static mkv_status fill_item(Cache *c, int layer, uint32_t first_pos, uint32_t pos, uint32_t ntok, const float *q, float *out,
+                            bool partial, VerifyItem *it) {
+    if (!c || !q || !out) {
+        set_error("null argument");
+        return MKV_ERR_INVALID;
+    }
+    if (layer < 0 || layer >= c->n_layers) {
+        set_error("layer %d outside [0, %d)", layer, c->n_layers);
+        return MKV_ERR_INVALID;
+    }
+    if (ntok < 1 || ntok > MKV_MAX_VERIFY) {
+        set_error("ntok %u outside [1, %d]", ntok, MKV_MAX_VERIFY);
+        return MKV_ERR_INVALID;
+    }
+    if (((uintptr_t)q & 15u) || ((uintptr_t)out & 7u)) {
+        set_error("q must be 16-byte aligned and out 8-byte aligned");
+        return MKV_ERR_INVALID;
+    }
+    const uint64_t end = (uint64_t)pos + ntok;
+    if (end > (uint64_t)MKV_CTX_MAX) {
+        set_error("pos %u + ntok %u exceeds the largest context %d", pos, ntok, MKV_CTX_MAX);
+        return MKV_ERR_CAPACITY;
+    }
+    if (first_pos > pos) {
+        set_error("first_pos %u > pos %u: token 0 would see no key", first_pos, pos);
+        return MKV_ERR_INVALID;
+    }
+    const uint32_t shard_end = c->shard_first + c->capacity;
+    if (!partial) {
+        if (c->shard_first != 0 || end > shard_end) {
+            set_error("keys [%u, %u) are not all in this cache [%u, %u): use mkv_attn_verify_partial on shards", first_pos,
+                      (uint32_t)end, c->shard_first, shard_end);
+            return c->shard_first != 0 ? MKV_ERR_INVALID : MKV_ERR_CAPACITY;
+        }
+    }
+    // rows that must be valid: the visible ones held here
+    const uint32_t need = (uint32_t)std::min<uint64_t>(end, shard_end);
+    if (need > c->shard_first && c->len < need) {
+        set_error("reads rows up to %u but only %u are valid (appended or restored)", need, c->len);
+        return MKV_ERR_STATE;
+    }
+    const uint32_t T = c->fmt == MKV_F16 ? TILE : TILE32;
+    const uint32_t lo = std::max(first_pos, c->shard_first);
+    const uint32_t hi = (uint32_t)std::min<uint64_t>(end, shard_end);
+    memset(it, 0, sizeof *it);
+    it->kmap = c->maps_dev + 2 * layer;
+    it->vmap = c->maps_dev + 2 * layer + 1;
+    it->kbuf = c->k[layer];
+    it->vbuf = c->v[layer];
+    it->q = q;
+    it->out = out;
+    it->first_pos = first_pos;
+    it->pos = pos;
+    it->ntok = ntok;
+    it->row0 = c->shard_first;
+    it->key_lo = c->shard_first;
+    it->key_hi = shard_end;
+    it->partial = partial ? 1u : 0u;
+    if (hi > lo) {
+        it->tile_begin = lo / T;
+        it->tile_end = (hi + T - 1) / T;
+    } else {
+        it->tile_begin = it->tile_end = 0;
+    }
+    return MKV_OK;
+}
+
+// Scratch regions per item, after planning.
+static mkv_status place_scratch(Cache *const *caches, VerifyItem *items, int n) {
+    // items of the same cache share its scratch; lay them out one after the other
+    for (int i = 0; i < n; i++) {
+        size_t before = 0;
+        for (int j = 0; j < i; j++)
+            if (caches[j] == caches[i]) before += 2u * (size_t)items[j].nsplit;
+        size_t total = before;
+        for (int j = i; j < n; j++)
+            if (caches[j] == caches[i]) total += 2u * (size_t)items[j].nsplit;
+        bool first = true;
+        for (int j = 0; j < i; j++)
+            if (caches[j] == caches[i]) first = false;
+        if (first) {
+            mkv_status st = ensure_scratch(caches[i], total);
+            if (st != MKV_OK) return st;
+        }
+        items[i].part_ml = caches[i]->part_ml + before * 32 * 2;
+        items[i].part_o = caches[i]->part_o + before * 32 * 256;
+    }
+    return MKV_OK;
+}
+
+static mkv_status verify_common(Cache *c, int layer, uint32_t first_pos, uint32_t pos, uint32_t ntok, const float *q,
+                                float *out, bool partial) {
+    VerifyItem it;
+    mkv_status st = fill_item(c, layer, first_pos, pos, ntok, q, out, partial, &it);
+    if (st != MKV_OK) return st;
+    if ((st = use_device(c->ctx)) != MKV_OK) return st;
+    plan_items(c->ctx, &it, 1);
+    Cache *cc[1] = {c};
+    if ((st = place_scratch(cc, &it, 1)) != MKV_OK) return st;
+    return launch_verify(c->ctx, c->fmt, &it, 1, false);
+}
+
+} // namespace mkv
+
+using namespace mkv;
+
+extern "C" {
+
+const char *mkv_strerror(mkv_status s) {
+    switch (s) {
+    case MKV_OK: return "ok";
+    case MKV_ERR_INVALID: return "invalid argument";
+    case MKV_ERR_CAPACITY: return "position outside the cache";
+    case MKV_ERR_CUDA: return "CUDA error";
+    case MKV_ERR_NOMEM: return "out of memory";
+    case MKV_ERR_UNSUPPORTED: return "not supported";
+    case MKV_ERR_STATE: return "rows not valid";
+    case MKV_ERR_FORMAT: return "format mismatch";
+    case MKV_ERR_IO: return "I/O error";
+    }
+    return "unknown status";
+}
+
+const char *mkv_last_error(void) { return g_err; }
+const char *mkv_version(void) { return "mechta-kv 0.1 sm_100a"; }
+
+mkv_status mkv_ctx_create(int device, void *stream, mkv_ctx **out) {
+    if (!out) {
+        set_error("null out");
+        return MKV_ERR_INVALID;
+    }
+    *out = nullptr;
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) {
+        cudaGetLastError();
+        set_error("no CUDA device: this library has no CPU path");
+        return MKV_ERR_CUDA;
+    }
+    if (device < 0 || device >= ndev) {
+        set_error("device %d outside [0, %d)", device, ndev);
+        return MKV_ERR_INVALID;
+    }
+    MKV_CUDA(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    MKV_CUDA(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10) {
+        set_error("device %d is sm_%d%d; this library is built for sm_100a only", device, prop.major, prop.minor);
+        return MKV_ERR_UNSUPPORTED;
+    }
+    Ctx *ctx = new (std::nothrow) Ctx();
+    if (!ctx) return MKV_ERR_NOMEM;
+    ctx->device = device;
+    ctx->sm_count = prop.multiProcessorCount;
+    if (stream) {
+        ctx->stream = (cudaStream_t)stream;
+    } else {
+        MKV_CUDA(cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking));
+        ctx->own_stream = true;
+    }
+    MKV_CUDA(cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking));
+    MKV_CUDA(cudaEventCreateWithFlags(&ctx->ev_compute, cudaEventDisableTiming));
+    MKV_CUDA(cudaEventCreateWithFlags(&ctx->ev_copy, cudaEventDisableTiming));
+    MKV_CUDA(cudaMalloc(&ctx->dev_status, 4));
+    MKV_CUDA(cudaMemset(ctx->dev_status, 0, 4));
+    const size_t ring = sizeof(VerifyItem) * (size_t)Ctx::SLOTS * Ctx::SLOT_ITEMS;
+    MKV_CUDA(cudaMalloc(&ctx->items_dev, ring));
+    MKV_CUDA(cudaHostAlloc(&ctx->items_host, ring, cudaHostAllocDefault));
+    for (int i = 0; i < Ctx::SLOTS; i++) MKV_CUDA(cudaEventCreateWithFlags(&ctx->slot_done[i], cudaEventDisableTiming));
+    mkv_status st = verify_setup_device();
+    if (st == MKV_OK) st = prefill_setup_device();
+    if (st != MKV_OK) return st;
+    *out = reinterpret_cast<mkv_ctx *>(ctx);
+    return MKV_OK;
+}
+
+void mkv_ctx_destroy(mkv_ctx *h) {
+    Ctx *ctx = reinterpret_cast<Ctx *>(h);
+    if (!ctx) return;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    cudaStreamSynchronize(ctx->copy_stream);
+    for (auto &p : ctx->prof_events) {
+        cudaEventDestroy(p.first);
+        cudaEventDestroy(p.second);
+    }
+    for (int i = 0; i < Ctx::SLOTS; i++)
+        if (ctx->slot_done[i]) cudaEventDestroy(ctx->slot_done[i]);
+    if (ctx->items_dev) cudaFree(ctx->items_dev);
+    if (ctx->items_host) cudaFreeHost(ctx->items_host);
+    if (ctx->dev_status) cudaFree(ctx->dev_status);
+    if (ctx->ev_compute) cudaEventDestroy(ctx->ev_compute);
+    if (ctx->ev_copy) cudaEventDestroy(ctx->ev_copy);
+    if (ctx->copy_stream) cudaStreamDestroy(ctx->copy_stream);
+    if (ctx->own_stream && ctx->stream) cudaStreamDestroy(ctx->stream);
+    delete ctx;
+}
+
+mkv_status mkv_sync(mkv_ctx *h) {
+    Ctx *ctx = reinterpret_cast<Ctx *>(h);
+    if (!ctx) {
+        set_error("null ctx");
+        return MKV_ERR_INVALID;
+    }
+    mkv_status st = use_device(ctx);
+    if (st != MKV_OK) return st;
+    MKV_CUDA(cudaStreamSynchronize(ctx->stream));
+    MKV_CUDA(cudaStreamSynchronize(ctx->copy_stream));
+    return check_device_status(ctx);
+}
+
+uint64_t mkv_launch_count(const mkv_ctx *h) { return h ? reinterpret_cast<const Ctx *>(h)->launches : 0; }
+
+mkv_status mkv_prof_enable(mkv_ctx *h, int on) {
+    Ctx *ctx = reinterpret_cast<Ctx *>(h);
+    if (!ctx) return MKV_ERR_INVALID;
+    ctx->prof = on != 0;
+    ctx->prof_used = 0;
+    return MKV_OK;
+}
+
+mkv_status mkv_prof_read(mkv_ctx *h, double *core_ms, uint64_t *core_launches) {
+    Ctx *ctx = reinterpret_cast<Ctx *>(h);
+    if (!ctx || !core_ms || !core_launches) return MKV_ERR_INVALID;
+    mkv_status st = use_device(ctx);
+    if (st != MKV_OK) return st;
+    double ms = 0.0;
+    if (ctx->prof_used > 0) MKV_CUDA(cudaEventSynchronize(ctx->prof_events[ctx->prof_used - 1].second));
+    for (size_t i = 0; i < ctx->prof_used; i++) {
+        float t = 0.f;
+        MKV_CUDA(cudaEventElapsedTime(&t, ctx->prof_events[i].first, ctx->prof_events[i].second));
+        ms += t;
+    }
+    *core_ms = ms;
+    *core_launches = ctx->prof_used;
+    ctx->prof_used = 0;
+    return MKV_OK;
+}
+
+uint64_t mkv_need_bytes(uint32_t ctx_tokens, mkv_fmt fmt, int n_layers) {
+    // M/engine.rs:63-67 buffer_bytes_for and M/memcheck.rs:15-18
+    const uint64_t ctx = ctx_tokens;
+    const uint64_t buf = 4ull * (fmt == MKV_F32 ? ctx * 512ull : ctx * 512ull / 2ull);
+    const uint64_t kv = 2ull * (uint64_t)n_layers * buf;
+    const uint64_t a = 8ull * (ctx / 64ull), b = 64ull * (ctx / 2048ull);
+    const uint64_t partials = 4ull * 258ull * 16ull * (2ull * (ctx / 128ull) + std::max(a, b));
+    return kv + partials;
+}
+
+mkv_status mkv_cache_create(mkv_ctx *h, mkv_fmt fmt, int n_layers, uint32_t capacity, uint32_t shard_first, mkv_cache **out) {
+    Ctx *ctx = reinterpret_cast<Ctx *>(h);
+    if (!ctx || !out) {
+        set_error("null argument");
+        return MKV_ERR_INVALID;
+    }
+    *out = nullptr;
+    if (fmt != MKV_F16 && fmt != MKV_F32) {
+        set_error("unknown format %d", (int)fmt);
+        return MKV_ERR_INVALID;
+    }
+    if (n_layers < 1 || n_layers > 256) {
+        set_error("n_layers %d outside [1, 256]", n_layers);
+        return MKV_ERR_INVALID;
+    }
+    if (shard_first == 0) {
+        // M/engine.rs:28-33 check_ctx
+        if (capacity % 1024 != 0 || capacity < MKV_CTX_MIN || capacity > MKV_CTX_MAX) {
+            set_error("context %u: must be a multiple of 1024 between %d and %d", capacity, MKV_CTX_MIN, MKV_CTX_MAX);
+            return MKV_ERR_INVALID;
+        }
+    } else if (capacity == 0 || capacity % 64 != 0 || shard_first % 64 != 0 ||
+               (uint64_t)shard_first + capacity > (uint64_t)MKV_CTX_MAX) {
+        set_error("shard [%u, +%u): first row and size must be multiples of 64 inside [0, %d]", shard_first, capacity,
+                  MKV_CTX_MAX);
+        return MKV_ERR_INVALID;
+    }
+    mkv_status st = use_device(ctx);
+    if (st != MKV_OK) return st;
+    Cache *c = new (std::nothrow) Cache();
+    if (!c) return MKV_ERR_NOMEM;
+    c->ctx = ctx;
+    c->fmt = fmt;
+    c->n_layers = n_layers;
+    c->capacity = capacity;
+    c->shard_first = shard_first;
+    c->elem = fmt == MKV_F16 ? 2 : 4;
+    c->buf_bytes = (size_t)capacity * ROW * c->elem;
+    c->k.assign(n_layers, nullptr);
+    c->v.assign(n_layers, nullptr);
+    auto fail = [&](mkv_status s) {
+        mkv_cache_destroy(reinterpret_cast<mkv_cache *>(c));
+        return s;
+    };
+    for (int l = 0; l < n_layers; l++) {
+        if (cudaMalloc(&c->k[l], c->buf_bytes) != cudaSuccess || cudaMalloc(&c->v[l], c->buf_bytes) != cudaSuccess) {
+            cudaGetLastError();
+            set_error("out of device memory for layer %d of %d (%zu bytes per buffer)", l, n_layers, c->buf_bytes);
+            return fail(MKV_ERR_NOMEM);
+        }
+        if (cudaMemsetAsync(c->k[l], 0, c->buf_bytes, ctx->stream) != cudaSuccess ||
+            cudaMemsetAsync(c->v[l], 0, c->buf_bytes, ctx->stream) != cudaSuccess) {
+            set_error("cudaMemsetAsync failed");
+            return fail(MKV_ERR_CUDA);
+        }
+    }
+    std::vector<CUtensorMap> maps(2 * (size_t)n_layers);
+    const uint32_t box_rows = fmt == MKV_F16 ? TILE : TILE32;
+    for (int l = 0; l < n_layers; l++) {
+        if ((st = make_tensor_map(&maps[2 * l], fmt, c->k[l], capacity, box_rows)) != MKV_OK) return fail(st);
+        if ((st = make_tensor_map(&maps[2 * l + 1], fmt, c->v[l], capacity, box_rows)) != MKV_OK) return fail(st);
+    }
+    if (cudaMalloc(&c->maps_dev, maps.size() * sizeof(CUtensorMap)) != cudaSuccess ||
+        cudaMalloc(&c->kptrs_dev, n_layers * sizeof(void *)) != cudaSuccess ||
+        cudaMalloc(&c->vptrs_dev, n_layers * sizeof(void *)) != cudaSuccess) {
+        cudaGetLastError();
+        set_error("out of device memory for the cache tables");
+        return fail(MKV_ERR_NOMEM);
+    }
+    if (cudaMemcpy(c->maps_dev, maps.data(), maps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice) != cudaSuccess ||
+        cudaMemcpy(c->kptrs_dev, c->k.data(), n_layers * sizeof(void *), cudaMemcpyHostToDevice) != cudaSuccess ||
+        cudaMemcpy(c->vptrs_dev, c->v.data(), n_layers * sizeof(void *), cudaMemcpyHostToDevice) != cudaSuccess ||
+        cudaEventCreateWithFlags(&c->ev_snapshot, cudaEventDisableTiming) != cudaSuccess) {
+        set_error("setting up the cache tables failed: %s", cudaGetErrorString(cudaGetLastError()));
+        return fail(MKV_ERR_CUDA);
+    }
+    if ((st = ensure_scratch(c, 2u * (size_t)ctx->sm_count)) != MKV_OK) return fail(st);
+    *out = reinterpret_cast<mkv_cache *>(c);
+    return MKV_OK;
+}
+
+void mkv_cache_destroy(mkv_cache *h) {
+    Cache *c = reinterpret_cast<Cache *>(h);
+    if (!c) return;
+    cudaSetDevice(c->ctx->device);
+    cudaStreamSynchronize(c->ctx->stream);
+    cudaStreamSynchronize(c->ctx->copy_stream);
+    for (void *p : c->k)
+        if (p) cudaFree(p);
+    for (void *p : c->v)
+        if (p) cudaFree(p);
+    if (c->maps_dev) cudaFree(c->maps_dev);
+    if (c->kptrs_dev) cudaFree(c->kptrs_dev);
+    if (c->vptrs_dev) cudaFree(c->vptrs_dev);
+    if (c->part_ml) cudaFree(c->part_ml);
+    if (c->part_o) cudaFree(c->part_o);
+    if (c->ev_snapshot) cudaEventDestroy(c->ev_snapshot);
+    delete c;
+}
+
+mkv_status mkv_cache_buffers(mkv_cache *h, int layer, void **k_dev, void **v_dev) {
+    Cache *c = reinterpret_cast<Cache *>(h);
+    if (!c || layer < 0 || layer >= c->n_layers) {
+        set_error("bad cache or layer");
+        return MKV_ERR_INVALID;
+    }
+    if (k_dev) *k_dev = c->k[layer];
+    if (v_dev) *v_dev = c->v[layer];
+    return MKV_OK;
+}
+
+uint32_t mkv_cache_len(const mkv_cache *h) { return h ? reinterpret_cast<const Cache *>(h)->len : 0; }
+
+mkv_status mkv_cache_set_len(mkv_cache *h, uint32_t len) {
+    Cache *c = reinterpret_cast<Cache *>(h);
+    if (!c) return MKV_ERR_INVALID;
+    if (len > c->shard_first + c->capacity) {
+        set_error("length %u beyond the end of the cache %u", len, c->shard_first + c->capacity);
+        return MKV_ERR_CAPACITY;
+    }
+    c->len = len;
+    return MKV_OK;
+}
+
+uint64_t mkv_cache_device_bytes(const mkv_cache *h) {
+    const Cache *c = reinterpret_cast<const Cache *>(h);
+    if (!c) return 0;
+    return 2ull * c->n_layers * c->buf_bytes + c->scratch_pieces * 32ull * 258ull * 4ull +
+           2ull * c->n_layers * (sizeof(CUtensorMap) + sizeof(void *));
+}
+
+void mkv_rope_table(int32_t pos, uint32_t ntok, float *out) {
+    // M/engine.rs:108-114: iterative theta, f32 libm
+    const float scale = powf(1e7f, -2.0f / 64.0f);
+    for (uint32_t t = 0; t < ntok; t++) {
+        float th = (float)(pos + (int32_t)t);
+        float *o = out + (size_t)t * 64;
+        for (int i = 0; i < 32; i++) {
+            o[i] = cosf(th);
+            o[32 + i] = sinf(th);
+            th *= scale;
+        }
+    }
+}
+
+static mkv_status append_common(Cache *c, int layer0, int n_layers, uint32_t pos, uint32_t ntok, const float *k,
+                                const float *v, const float *tab) {
+    if (!c || !k || !v) {
+        set_error("null argument");
+        return MKV_ERR_INVALID;
+    }
+    if (ntok < 1 || ntok > 4096) {
+        set_error("ntok %u outside [1, 4096]", ntok);
+        return MKV_ERR_INVALID;
+    }
+    if (((uintptr_t)k & 15u) || ((uintptr_t)v & 15u) || ((uintptr_t)tab & 15u)) {
+        set_error("k, v and the rope table must be 16-byte aligned");
+        return MKV_ERR_INVALID;
+    }
+    const uint64_t end = (uint64_t)pos + ntok;
+    const uint32_t shard_end = c->shard_first + c->capacity;
+    if (c->shard_first == 0 ? end > shard_end : end > (uint64_t)MKV_CTX_MAX) {
+        set_error("rows [%u, %u) do not fit the cache of %u rows", pos, (uint32_t)end, c->capacity);
+        return MKV_ERR_CAPACITY;
+    }
+    mkv_status st = use_device(c->ctx);
+    if (st != MKV_OK) return st;
+    st = launch_append(c->ctx, c->fmt, c->kptrs_dev + layer0, c->vptrs_dev + layer0, n_layers, (size_t)ntok * ROW,
+                       c->shard_first, c->capacity, pos, ntok, k, v, tab, 3u);
+    if (st != MKV_OK) return st;
+    c->len = (uint32_t)std::min<uint64_t>(end, shard_end);
+    if (c->len < c->shard_first) c->len = c->shard_first;
+    return MKV_OK;
+}
+
+mkv_status mkv_append(mkv_cache *h, int layer, uint32_t pos, uint32_t ntok, const float *k, const float *v, const float *tab) {
+    Cache *c = reinterpret_cast<Cache *>(h);
+    if (!c || layer < 0 || layer >= c->n_layers) {
+        set_error("bad cache or layer %d", layer);
+        return MKV_ERR_INVALID;
+    }
+    return append_common(c, layer, 1, pos, ntok, k, v, tab);
+}
+
+mkv_status mkv_append_layers(mkv_cache *h, uint32_t pos, uint32_t ntok, const float *k, const float *v, const float *tab) {
+    Cache *c = reinterpret_cast<Cache *>(h);
+    if (!c) {
+        set_error("null cache");
+        return MKV_ERR_INVALID;
+    }
+    return append_common(c, 0, c->n_layers, pos, ntok, k, v, tab);
+}
+
+mkv_status mkv_truncate(mkv_cache *h, uint32_t new_len, int scrub) {
+    Cache *c = reinterpret_cast<Cache *>(h);
+    if (!c) {
+        set_error("null cache");
+        return MKV_ERR_INVALID;
+    }
+    if (new_len > c->len) {
+        set_error("cannot truncate to %u: only %u rows are valid", new_len, c->len);
+        return MKV_ERR_STATE;
+    }
+    const uint32_t old = c->len;
+    c->len = std::max(new_len, std::min(c->shard_first, old));
+    if (scrub && old > c->len) {
+        mkv_status st = use_device(c->ctx);
+        if (st != MKV_OK) return st;
+        const size_t off = (size_t)(c->len - c->shard_first) * ROW * c->elem;
+        const size_t nb = (size_t)(old - c->len) * ROW * c->elem;
+        for (int l = 0; l < c->n_layers; l++) {
+            MKV_CUDA(cudaMemsetAsync((char *)c->k[l] + off, 0, nb, c->ctx->stream));
+            MKV_CUDA(cudaMemsetAsync((char *)c->v[l] + off, 0, nb, c->ctx->stream));
+        }
+    }
+    return MKV_OK;
+}
+
+mkv_status mkv_attn_verify(mkv_cache *h, int layer, uint32_t first_pos, uint32_t pos, uint32_t ntok, const float *q, float *out) {
+    return verify_common(reinterpret_cast<Cache *>(h), layer, first_pos, pos, ntok, q, out, false);
+}
+
+mkv_status mkv_attn_verify_partial(mkv_cache *h, int layer, uint32_t first_pos, uint32_t pos, uint32_t ntok, const float *q,
+                                   float *rec) {
+    return verify_common(reinterpret_cast<Cache *>(h), layer, first_pos, pos, ntok, q, rec, true);
+}
+
+mkv_status mkv_combine_shards(mkv_ctx *h, const float *recs, int n_shards, uint32_t ntok, float *out) {
+    Ctx *ctx = reinterpret_cast<Ctx *>(h);
+    if (!ctx || !recs || !out || n_shards < 1 || ntok < 1 || ntok > MKV_MAX_VERIFY) {
+        set_error("bad argument to mkv_combine_shards");
+        return MKV_ERR_INVALID;
+    }
+    mkv_status st = use_device(ctx);
+    if (st != MKV_OK) return st;
+    return launch_combine_shards(ctx, recs, n_shards, ntok, out);
+}
+
+mkv_status mkv_attn_verify_batch(mkv_ctx *h, const mkv_verify_item *items, int n) {
+    Ctx *ctx = reinterpret_cast<Ctx *>(h);
+    if (!ctx || !items || n < 1 || n > Ctx::SLOT_ITEMS) {
+        set_error("bad argument to mkv_attn_verify_batch (1 <= n <= %d)", Ctx::SLOT_ITEMS);
+        return MKV_ERR_INVALID;
+    }
+    std::vector<VerifyItem> its((size_t)n);
+    std::vector<Cache *> caches((size_t)n);
+    mkv_fmt fmt = MKV_F16;
+    for (int i = 0; i < n; i++) {
+        Cache *c = reinterpret_cast<Cache *>(items[i].cache);
+        if (!c || c->ctx != ctx) {
+            set_error("item %d: cache missing or of another context", i);
+            return MKV_ERR_INVALID;
+        }
+        if (i == 0) fmt = c->fmt;
+        else if (c->fmt != fmt) {
+            set_error("item %d: all caches of a batch must have one format", i);
+            return MKV_ERR_INVALID;
+        }
+        mkv_status st = fill_item(c, items[i].layer, items[i].first_pos, items[i].pos, items[i].ntok, items[i].q_dev,
+                                  items[i].out_dev, false, &its[i]);
+        if (st != MKV_OK) return st;
+        caches[i] = c;
+    }
+    mkv_status st = use_device(ctx);
+    if (st != MKV_OK) return st;
+    plan_items(ctx, its.data(), n);
+    if ((st = place_scratch(caches.data(), its.data(), n)) != MKV_OK) return st;
+    return launch_verify(ctx, fmt, its.data(), n, true);
+}
+
+mkv_status mkv_attn_prefill(mkv_cache *h, int layer, uint32_t first_pos, uint32_t pos0, uint32_t ntok, const float *q,
+                            float *out) {
+    Cache *c = reinterpret_cast<Cache *>(h);
+    if (!c || !q || !out || layer < 0 || layer >= c->n_layers) {
+        set_error("bad argument to mkv_attn_prefill");
+        return MKV_ERR_INVALID;
+    }
+    if (ntok < 1 || ntok > 4096) {
+        set_error("ntok %u outside [1, 4096]", ntok);
+        return MKV_ERR_INVALID;
+    }
+    if (((uintptr_t)q & 15u) || ((uintptr_t)out & 15u)) {
+        set_error("q and out must be 16-byte aligned");
+        return MKV_ERR_INVALID;
+    }
+    if (c->shard_first != 0) {
+        set_error("prefill attention runs on unsharded caches");
+        return MKV_ERR_UNSUPPORTED;
+    }
+    const uint64_t end = (uint64_t)pos0 + ntok;
+    if (end > c->capacity) {
+        set_error("rows [%u, %u) do not fit the cache of %u rows", pos0, (uint32_t)end, c->capacity);
+        return MKV_ERR_CAPACITY;
+    }
+    if (first_pos > pos0) {
+        set_error("first_pos %u > pos0 %u", first_pos, pos0);
+        return MKV_ERR_INVALID;
+    }
+    if (c->len < end) {
+        set_error("reads rows up to %u but only %u are valid: append the block first", (uint32_t)end, c->len);
+        return MKV_ERR_STATE;
+    }
+    mkv_status st = use_device(c->ctx);
+    if (st != MKV_OK) return st;
+    if (c->fmt == MKV_F16) return launch_prefill_f16_mma(c->ctx, c, layer, first_pos, pos0, ntok, q, out);
+    // f32 cache: groups of up to 4 tokens through the f32 verify kernel (the reference's attn_fd4 also reads
+    // K/V once per 4 tokens, W/ops.wgsl:694-699), one ragged batch per <= SLOT_ITEMS groups
+    uint32_t done = 0;
+    while (done < ntok) {
+        const uint32_t left = ntok - done;
+        const int groups = (int)std::min<uint32_t>((left + 3) / 4, Ctx::SLOT_ITEMS);
+        std::vector<VerifyItem> its((size_t)groups);
+        std::vector<Cache *> caches((size_t)groups, c);
+        for (int g = 0; g < groups; g++) {
+            const uint32_t t = done + 4u * g;
+            const uint32_t nt = std::min<uint32_t>(4, ntok - t);
+            st = fill_item(c, layer, first_pos, pos0 + t, nt, q + (size_t)t * 4096, out + (size_t)t * 4096, false, &its[g]);
+            if (st != MKV_OK) return st;
+        }
+        plan_items(c->ctx, its.data(), groups);
+        if ((st = place_scratch(caches.data(), its.data(), groups)) != MKV_OK) return st;
+        if ((st = launch_verify(c->ctx, c->fmt, its.data(), groups, true)) != MKV_OK) return st;
+        done += 4u * groups;
+    }
+    return MKV_OK;
+}
+
+// ---- snapshot / restore -------------------------------------------------------------------------------------
+
+// rows of [0, p) this cache holds: [r0, r1) in global positions
+static void held_rows(const Cache *c, uint32_t p, uint32_t *r0, uint32_t *r1) {
+    const uint32_t end = c->shard_first + c->capacity;
+    *r0 = std::min(c->shard_first, p);
+    *r1 = std::min(p, end);
+    if (*r1 < *r0) *r1 = *r0;
+}
+
+size_t mkv_snapshot_bytes(const mkv_cache *h, uint32_t p) {
+    const Cache *c = reinterpret_cast<const Cache *>(h);
+    if (!c) return 0;
+    uint32_t r0, r1;
+    held_rows(c, p, &r0, &r1);
+    return 2ull * c->n_layers * (size_t)(r1 - r0) * ROW * c->elem;
+}
+
+mkv_status mkv_snapshot(mkv_cache *h, uint32_t p, void *dst, size_t cap, size_t *written) {
+    Cache *c = reinterpret_cast<Cache *>(h);
+    if (!c || !dst) {
+        set_error("null argument");
+        return MKV_ERR_INVALID;
+    }
+    if (p > c->len) {
+        set_error("snapshot of %u rows but only %u are valid", p, c->len);
+        return MKV_ERR_STATE;
+    }
+    const size_t need = mkv_snapshot_bytes(h, p);
+    if (cap < need) {
+        set_error("snapshot needs %zu bytes, buffer has %zu", need, cap);
+        return MKV_ERR_INVALID;
+    }
+    Ctx *ctx = c->ctx;
+    mkv_status st = use_device(ctx);
+    if (st != MKV_OK) return st;
+    uint32_t r0, r1;
+    held_rows(c, p, &r0, &r1);
+    const size_t nb = (size_t)(r1 - r0) * ROW * c->elem;
+    const size_t off = (size_t)(r0 - c->shard_first) * ROW * c->elem;
+    // the copies start after what is already enqueued on the compute stream
+    MKV_CUDA(cudaEventRecord(ctx->ev_compute, ctx->stream));
+    MKV_CUDA(cudaStreamWaitEvent(ctx->copy_stream, ctx->ev_compute, 0));
+    char *d = static_cast<char *>(dst);
+    if (nb > 0)
+        for (int l = 0; l < c->n_layers; l++) {
+            MKV_CUDA(cudaMemcpyAsync(d, (const char *)c->k[l] + off, nb, cudaMemcpyDeviceToHost, ctx->copy_stream));
+            d += nb;
+            MKV_CUDA(cudaMemcpyAsync(d, (const char *)c->v[l] + off, nb, cudaMemcpyDeviceToHost, ctx->copy_stream));
+            d += nb;
+        }
+    MKV_CUDA(cudaEventRecord(c->ev_snapshot, ctx->copy_stream));
+    c->snapshot_pending = true;
+    // later appends must not overwrite rows still being copied out
+    MKV_CUDA(cudaEventRecord(ctx->ev_copy, ctx->copy_stream));
+    MKV_CUDA(cudaStreamWaitEvent(ctx->stream, ctx->ev_copy, 0));
+    if (written) *written = need;
+    return MKV_OK;
+}
+
+mkv_status mkv_snapshot_wait(mkv_cache *h) {
+    Cache *c = reinterpret_cast<Cache *>(h);
+    if (!c) return MKV_ERR_INVALID;
+    if (c->snapshot_pending) {
+        mkv_status st = use_device(c->ctx);
+        if (st != MKV_OK) return st;
+        MKV_CUDA(cudaEventSynchronize(c->ev_snapshot));
+        c->snapshot_pending = false;
+    }
+    return MKV_OK;
+}
+
+mkv_status mkv_restore(mkv_cache *h, uint32_t p, const void *src, size_t bytes) {
+    Cache *c = reinterpret_cast<Cache *>(h);
+    if (!c || !src) {
+        set_error("null argument");
+        return MKV_ERR_INVALID;
+    }
+    const uint32_t end = c->shard_first + c->capacity;
+    if (c->shard_first == 0 && p > end) {
+        set_error("restore of %u rows into a cache of %u", p, c->capacity);
+        return MKV_ERR_CAPACITY;
+    }
+    const size_t need = mkv_snapshot_bytes(h, p);
+    if (bytes != need) {
+        set_error("restore payload is %zu bytes, %u rows of this cache are %zu", bytes, p, need);
+        return MKV_ERR_FORMAT;
+    }
+    Ctx *ctx = c->ctx;
+    mkv_status st = use_device(ctx);
+    if (st != MKV_OK) return st;
+    uint32_t r0, r1;
+    held_rows(c, p, &r0, &r1);
+    const size_t nb = (size_t)(r1 - r0) * ROW * c->elem;
+    const size_t off = (size_t)(r0 - c->shard_first) * ROW * c->elem;
+    MKV_CUDA(cudaEventRecord(ctx->ev_compute, ctx->stream));
+    MKV_CUDA(cudaStreamWaitEvent(ctx->copy_stream, ctx->ev_compute, 0));
+    const char *s = static_cast<const char *>(src);
+    if (nb > 0)
+        for (int l = 0; l < c->n_layers; l++) {
+            MKV_CUDA(cudaMemcpyAsync((char *)c->k[l] + off, s, nb, cudaMemcpyHostToDevice, ctx->copy_stream));
+            s += nb;
+            MKV_CUDA(cudaMemcpyAsync((char *)c->v[l] + off, s, nb, cudaMemcpyHostToDevice, ctx->copy_stream));
+            s += nb;
+        }
+    MKV_CUDA(cudaEventRecord(ctx->ev_copy, ctx->copy_stream));
+    MKV_CUDA(cudaStreamWaitEvent(ctx->stream, ctx->ev_copy, 0));
+    c->len = std::max(r1, std::min(c->shard_first, p));
+    return MKV_OK;
+}
+
+mkv_status mkv_host_alloc(size_t bytes, void **out) {
+    if (!out) return MKV_ERR_INVALID;
+    *out = nullptr;
+    if (cudaHostAlloc(out, bytes ? bytes : 1, cudaHostAllocDefault) != cudaSuccess) {
+        cudaGetLastError();
+        set_error("cudaHostAlloc of %zu bytes failed", bytes);
+        return MKV_ERR_NOMEM;
+    }
+    return MKV_OK;
+}
+
+void mkv_host_free(void *p) {
+    if (p) cudaFreeHost(p);
+}
+
+// ---- the reference's dispatch form --------------------------------------------------------------------------
+
+mkv_status mkv_dispatch(mkv_cache *h, int layer, const char *op, const uint32_t u[8], const void *in0, const void *in1,
+                        void *out) {
+    Cache *c = reinterpret_cast<Cache *>(h);
+    if (!c || !op || !u) {
+        set_error("null argument");
+        return MKV_ERR_INVALID;
+    }
+    const bool f16 = c->fmt == MKV_F16;
+    auto is = [&](const char *a) { return strcmp(op, a) == 0; };
+    // P{n, rows, f0, f1, step_a, step_o, flag, extra} (W/ops.wgsl:4)
+    const uint32_t n = u[0], rows = u[1], f0 = u[2], f1 = u[3], step_a = u[4], step_o = u[5], flag = u[6], extra = u[7];
+    float scale;
+    memcpy(&scale, &f0, 4);
+    if (is("kv_rope") || is("kv_rope2") || is("rope") || is("rope2")) {
+        const bool compact = op[0] == 'k';
+        if (compact != f16) {
+            set_error("%s is the writer of the %s cache (M/engine.rs:100-105)", op, compact ? "f16" : "f32");
+            return MKV_ERR_INVALID;
+        }
+        if (n != 256 || step_a != 256 || step_o != 256 || extra % 512 != 0 || rows % 2 != 0 || rows == 0) {
+            set_error("%s: only the KV writer form [256, 2*ntok, 0,0, 256,256, flag, pos*512] is built", op);
+            return MKV_ERR_UNSUPPORTED;
+        }
+        const bool multi = is("kv_rope2") || is("rope2");
+        if (multi ? flag != 2 : rows != 2) {
+            set_error("%s: rows per token must be 2", op);
+            return MKV_ERR_UNSUPPORTED;
+        }
+        const uint32_t ntok = rows / 2, pos = extra / 512;
+        if (!in0 || !in1 || layer < 0 || layer >= c->n_layers) {
+            set_error("%s: missing binding or bad layer", op);
+            return MKV_ERR_INVALID;
+        }
+        if ((uint64_t)pos + ntok > c->capacity) {
+            set_error("rows [%u, %u) do not fit the cache of %u rows", pos, pos + ntok, c->capacity);
+            return MKV_ERR_CAPACITY;
+        }
+        mkv_status st = use_device(c->ctx);
+        if (st != MKV_OK) return st;
+        return launch_append(c->ctx, c->fmt, c->kptrs_dev + layer, c->vptrs_dev + layer, 1, (size_t)ntok * ROW,
+                             c->shard_first, c->capacity, pos, ntok, (const float *)in0, (const float *)in0,
+                             (const float *)in1, 1u);
+    }
+    if (is("kv_copy") || is("copy")) {
+        const bool compact = op[0] == 'k';
+        if (compact != f16) {
+            set_error("%s is the writer of the %s cache (M/engine.rs:100-105)", op, compact ? "f16" : "f32");
+            return MKV_ERR_INVALID;
+        }
+        if (n == 0 || n % 512 != 0 || extra % 512 != 0) {
+            set_error("%s: only whole positions are written (n and extra multiples of 512)", op);
+            return MKV_ERR_UNSUPPORTED;
+        }
+        const uint32_t ntok = n / 512, pos = extra / 512;
+        if (!in0 || layer < 0 || layer >= c->n_layers) {
+            set_error("%s: missing binding or bad layer", op);
+            return MKV_ERR_INVALID;
+        }
+        if ((uint64_t)pos + ntok > c->capacity) {
+            set_error("rows [%u, %u) do not fit the cache of %u rows", pos, pos + ntok, c->capacity);
+            return MKV_ERR_CAPACITY;
+        }
+        mkv_status st = use_device(c->ctx);
+        if (st != MKV_OK) return st;
+        st = launch_append(c->ctx, c->fmt, c->kptrs_dev + layer, c->vptrs_dev + layer, 1, (size_t)ntok * ROW, c->shard_first,
+                           c->capacity, pos, ntok, (const float *)in0, (const float *)in0, nullptr, 2u);
+        // the V writer is the second of the pair (M/quad.rs:116-117): the rows are now complete
+        if (st == MKV_OK) c->len = pos + ntok;
+        return st;
+    }
+    if (is("q_dmx") || is("attn_fd_combine") || is("q_f16")) return MKV_OK; // fused into the attention entry
+    if (is("attn_dmx1") || is("attn_dmx2") || is("attn_fd") || is("attn_fd2h")) {
+        if (fabsf(scale - SCALE) > 0.f) {
+            set_error("%s: scale %g, only 1/16 is built", op, scale);
+            return MKV_ERR_UNSUPPORTED;
+        }
+        uint32_t ntok, first = extra;
+        if (is("attn_dmx1") || is("attn_dmx2")) {
+            ntok = f1; // uniform [pos+1, chunks, scale, ntok, 0, 0, chunk, 0] (M/quad.rs:286)
+            if (!f16) {
+                set_error("%s runs on the f16 cache only (M/dmx.rs:2)", op);
+                return MKV_ERR_INVALID;
+            }
+            if (ntok < 1 || ntok > (is("attn_dmx1") ? 2u : 4u)) return MKV_ERR_INVALID;
+        } else if (is("attn_fd2h")) {
+            ntok = 2;
+        } else {
+            ntok = step_o > 0 ? step_o : 1; // decode: one token per grid z; here one call per token group
+            if (ntok > 4) {
+                set_error("attn_fd in prefill mode (step_o = %u): use mkv_attn_prefill", step_o);
+                return MKV_ERR_UNSUPPORTED;
+            }
+        }
+        (void)rows;
+        (void)step_a;
+        (void)flag;
+        if (n == 0) return MKV_ERR_INVALID;
+        return mkv_attn_verify(h, layer, first, n - 1, ntok, (const float *)in0, (float *)out);
+    }
+    set_error("dispatch of '%s' is outside the KV path", op);
+    return MKV_ERR_UNSUPPORTED;
+}
+
+} // extern "C"

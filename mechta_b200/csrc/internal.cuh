@@ -1,0 +1,119 @@
+// Internal declarations shared by the kernels and the C-ABI host code of libmechta_kv.
+#pragma once
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+#include <vector>
+
+#include "../../include/mechta_kv.h"
+
+namespace mkv {
+
+constexpr int HQ = 16, HKV = 2, D = 256, GROUP = 8, ROW = 512, REC = 258;
+constexpr int TILE = 64;            // keys per attention tile, f16 cache (as the reference, M/dmx.rs:53)
+constexpr int TILE32 = 32;          // keys per tile, f32 cache
+constexpr float NEG_BIG = -3.0e38f; // mask value of the reference (W/ops.wgsl:339)
+constexpr float NEG_TEST = -1.0e38f;
+constexpr float SCALE = 1.0f / 16.0f; // M/quad.rs:286 bits(1/16)
+constexpr int MAX_SPLITS = 160;     // upper bound of split-K pieces per KV head of one item
+
+// status word written by kernels instead of trapping (bit set = what went wrong)
+enum : uint32_t { DEV_ERR_WAIT_TIMEOUT = 1u, DEV_ERR_RANGE = 2u };
+
+void set_error(const char *fmt, ...);
+
+#define MKV_CUDA(expr)                                                                         \
+    do {                                                                                       \
+        cudaError_t e__ = (expr);                                                              \
+        if (e__ != cudaSuccess) {                                                              \
+            mkv::set_error("%s: %s (%s:%d)", #expr, cudaGetErrorString(e__), __FILE__, __LINE__); \
+            return MKV_ERR_CUDA;                                                               \
+        }                                                                                      \
+    } while (0)
+
+// One split-K work item of the verify attention: everything a CTA needs, in device memory or in the
+// kernel's parameter space.
+struct VerifyItem {
+    const CUtensorMap *kmap; // device address of the layer's K tensor map
+    const CUtensorMap *vmap;
+    const void *kbuf; // raw buffers (kernels that do not use TMA)
+    const void *vbuf;
+    const float *q; // [ntok][16][256]
+    float *out;     // [ntok][16][256], or the [64][258] record in partial mode
+    float *part_ml; // [2][nsplit][32][2]
+    float *part_o;  // [2][nsplit][32][256]
+    uint32_t first_pos, pos, ntok;
+    uint32_t row0;     // global position of the cache's first row (shard_first)
+    uint32_t key_lo;   // visible keys are key_lo <= key < min(key_hi, pos+1+tok)
+    uint32_t key_hi;
+    uint32_t tile_begin, tile_end; // absolute tile range [tile_begin, tile_end), tile j = keys [T*j, T*j+T)
+    uint32_t nsplit;               // pieces per KV head
+    uint32_t tiles_per_split;
+    uint32_t cta_begin; // first CTA of this item in the flattened grid (2 * nsplit CTAs per item)
+    uint32_t partial;   // 1: write the un-normalised record instead of the final output
+};
+
+struct Ctx;
+struct Cache;
+
+struct Ctx {
+    int device = 0;
+    int sm_count = 148;
+    cudaStream_t stream = nullptr;
+    bool own_stream = false;
+    cudaStream_t copy_stream = nullptr;
+    cudaEvent_t ev_compute = nullptr; // compute -> copy ordering
+    cudaEvent_t ev_copy = nullptr;    // copy -> compute ordering
+    uint32_t *dev_status = nullptr;   // device status word
+    uint64_t launches = 0;
+    // profiling of the attention core kernels
+    bool prof = false;
+    std::vector<std::pair<cudaEvent_t, cudaEvent_t>> prof_events;
+    size_t prof_used = 0;
+    // staging ring for batched items: pinned host slots, device slots, one event per slot
+    static constexpr int SLOTS = 8;
+    static constexpr int SLOT_ITEMS = 1024;
+    VerifyItem *items_dev = nullptr;  // [SLOTS][SLOT_ITEMS]
+    VerifyItem *items_host = nullptr; // pinned, same shape
+    cudaEvent_t slot_done[SLOTS] = {};
+    bool slot_used[SLOTS] = {};
+    int slot_next = 0;
+};
+
+struct Cache {
+    Ctx *ctx = nullptr;
+    mkv_fmt fmt = MKV_F16;
+    int n_layers = 0;
+    uint32_t capacity = 0;
+    uint32_t shard_first = 0;
+    uint32_t len = 0; // global position after the last valid row
+    size_t elem = 2;
+    size_t buf_bytes = 0;
+    std::vector<void *> k, v;
+    void **kptrs_dev = nullptr;      // [n_layers] device copies of k / v
+    void **vptrs_dev = nullptr;
+    CUtensorMap *maps_dev = nullptr; // [n_layers][2]: verify tiles; [n_layers][2] more: none yet
+    float *part_ml = nullptr;        // split-K scratch, shared by the layers (stream-ordered), grow-only
+    float *part_o = nullptr;
+    size_t scratch_pieces = 0;       // pieces (KV head x split) the scratch holds
+    cudaEvent_t ev_snapshot = nullptr;
+    bool snapshot_pending = false;
+};
+
+// ---- launchers (defined in the .cu files) ---------------------------------------------------------------
+mkv_status launch_append(Ctx *ctx, mkv_fmt fmt, void *const *kbufs, void *const *vbufs, int n_layers,
+                         size_t layer_stride_in, uint32_t row_first, uint32_t capacity, uint32_t pos, uint32_t ntok,
+                         const float *k, const float *v, const float *tab, uint32_t which /*1 = K, 2 = V, 3 = both*/);
+// items_host[0..n) are planned; batch = false: n == 1 and the item travels in the kernel's parameter space
+mkv_status launch_verify(Ctx *ctx, mkv_fmt fmt, const VerifyItem *items_host, int n, bool batch);
+mkv_status verify_setup_device();
+mkv_status launch_combine_shards(Ctx *ctx, const float *recs, int n_shards, uint32_t ntok, float *out);
+mkv_status launch_prefill(Ctx *ctx, Cache *c, int layer, uint32_t first_pos, uint32_t pos0, uint32_t ntok,
+                          const float *q, float *out);
+// plans the split of the items so that the grid fills the SMs once
+void plan_items(Ctx *ctx, VerifyItem *items, int n);
+
+} // namespace mkv

@@ -1,0 +1,471 @@
+// Decode / verify attention over the f16 cache: split-K flash-decode for up to 4 tokens x 8 query heads
+// (32 rows) per KV head, then a log-sum-exp combine of the pieces.
+//
+// Stands in for q_dmx + attn_dmx2 + attn_fd_combine of the reference (M/dmx.rs:19-141, W/ops.wgsl:523-538):
+// same visibility rule (token t at pos + t sees first_pos <= key < pos + 1 + t), same mask value, same
+// un-normalised partial [m, l, O] per piece, one divide at the end. What differs is the machine mapping:
+//  - a CTA owns one KV head and a contiguous run of 64-key tiles; K and V tiles arrive by TMA
+//    (cp.async.bulk.tensor, 128-byte swizzle, no multicast) into a 3-deep ring of 64 KB stages, each filled
+//    tile signalled on an mbarrier;
+//  - S = Q K^T: warp w takes keys 8w..8w+7 of the tile for all 32 rows (mma.m16n8k16, Q fragments live in
+//    registers as f16), so every K byte is read from shared memory once;
+//  - softmax: 8 threads per row, max and sum by warp shuffles, P rounded to f16 (as the reference does) and
+//    the row sum taken over the rounded values;
+//  - O += P V: warp w owns dims 32w..32w+31 for all rows, so every V byte is read from shared memory once.
+#include <string.h>
+
+#include "internal.cuh"
+#include "ptx.cuh"
+
+namespace mkv {
+using namespace ptx;
+
+constexpr int V16_NST = 3;                       // ring depth
+constexpr uint32_t V16_STAGE = 65536;            // K 32 KB + V 32 KB
+constexpr uint32_t V16_SUB = 8192;               // one [64 keys][64 dims] f16 sub-box
+constexpr uint32_t V16_OFF_Q = V16_NST * V16_STAGE;
+constexpr uint32_t V16_OFF_S = V16_OFF_Q + 32 * 512;
+constexpr uint32_t V16_S_STRIDE = 68;            // floats per S row (64 + 4 of padding)
+constexpr uint32_t V16_OFF_P = V16_OFF_S + 32 * V16_S_STRIDE * 4;
+constexpr uint32_t V16_OFF_CF = V16_OFF_P + 32 * 128;
+constexpr uint32_t V16_OFF_BAR = V16_OFF_CF + 32 * 4;
+constexpr uint32_t V16_SMEM = V16_OFF_BAR + V16_NST * 8 + 1024; // + alignment slack
+constexpr long long WAIT_LIMIT = 4000000000ll;   // about two seconds of SM clocks
+
+__device__ __forceinline__ const VerifyItem &pick_item(const VerifyItem *items, int n_items, const VerifyItem &single,
+                                                       uint32_t cta) {
+    if (items == nullptr) return single;
+    int lo = 0;
+    for (int i = 1; i < n_items; i++)
+        if (cta >= items[i].cta_begin) lo = i;
+    return items[lo];
+}
+
+__global__ void __launch_bounds__(256, 1)
+verify_f16_kernel(const VerifyItem *__restrict__ items, int n_items, const __grid_constant__ VerifyItem single,
+                  uint32_t *__restrict__ status) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *smem = smem_raw + (smem_base - smem_u32(smem_raw));
+
+    const VerifyItem &it = pick_item(items, n_items, single, blockIdx.x);
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+    const uint32_t local = blockIdx.x - it.cta_begin;
+    if (local >= 2u * it.nsplit) return;
+    const uint32_t kvh = local & 1u, split = local >> 1;
+    const uint32_t t0 = it.tile_begin + split * it.tiles_per_split;
+    const uint32_t t1 = min(t0 + it.tiles_per_split, it.tile_end);
+    const uint32_t nt = t1 - t0;
+    const CUtensorMap *kmap = it.kmap, *vmap = it.vmap;
+    const uint32_t bar0 = smem_base + V16_OFF_BAR;
+
+    if (tid == 0) {
+        for (int s = 0; s < V16_NST; s++) mbar_init(bar0 + 8u * s, 1);
+        fence_barrier_init();
+        fence_proxy_async();
+    }
+    __syncthreads();
+
+    auto issue = [&](uint32_t j) { // thread 0 only: tile j of this CTA into stage j % NST
+        const uint32_t s = j % V16_NST, bar = bar0 + 8u * s;
+        const uint32_t dst = smem_base + s * V16_STAGE;
+        const int y = (int)((t0 + j) * TILE - it.row0);
+        const int x = (int)(kvh * 256u);
+        mbar_expect_tx(bar, V16_STAGE);
+#pragma unroll
+        for (int sb = 0; sb < 4; sb++) tma_load_2d(dst + sb * V16_SUB, kmap, x + 64 * sb, y, bar);
+#pragma unroll
+        for (int sb = 0; sb < 4; sb++) tma_load_2d(dst + 4 * V16_SUB + sb * V16_SUB, vmap, x + 64 * sb, y, bar);
+    };
+    if (tid == 0) {
+        const uint32_t pre = nt < (uint32_t)V16_NST ? nt : (uint32_t)V16_NST;
+        for (uint32_t j = 0; j < pre; j++) issue(j);
+    }
+
+    // Q of this KV head to shared memory as f16: row = tok * 8 + head % 8 (the order of q_dmx, M/dmx.rs:128-138),
+    // rows of tokens >= ntok zero; 16-byte chunks swizzled inside each 128-byte group
+    {
+        uint8_t *qs = smem + V16_OFF_Q;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const uint32_t idx = tid + 256u * i; // 32 rows x 32 chunks of 8 dims
+            const uint32_t row = idx >> 5, chunk = idx & 31u;
+            uint4 w = make_uint4(0, 0, 0, 0);
+            const uint32_t tok = row >> 3;
+            if (tok < it.ntok) {
+                const float *src = it.q + (size_t)tok * 4096u + (size_t)(8u * kvh + (row & 7u)) * 256u + chunk * 8u;
+                const float4 a = *reinterpret_cast<const float4 *>(src);
+                const float4 b = *reinterpret_cast<const float4 *>(src + 4);
+                __half2 h0 = __floats2half2_rn(a.x, a.y), h1 = __floats2half2_rn(a.z, a.w);
+                __half2 h2 = __floats2half2_rn(b.x, b.y), h3 = __floats2half2_rn(b.z, b.w);
+                w.x = *reinterpret_cast<uint32_t *>(&h0);
+                w.y = *reinterpret_cast<uint32_t *>(&h1);
+                w.z = *reinterpret_cast<uint32_t *>(&h2);
+                w.w = *reinterpret_cast<uint32_t *>(&h3);
+            }
+            const uint32_t pc = (chunk & ~7u) | ((chunk ^ row) & 7u);
+            *reinterpret_cast<uint4 *>(qs + row * 512u + pc * 16u) = w;
+        }
+    }
+    __syncthreads();
+
+    // A fragments of Q for both 16-row tiles and all 16 k-steps
+    uint32_t qf[2][16][4];
+    {
+        const uint32_t qs = smem_base + V16_OFF_Q;
+#pragma unroll
+        for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+            for (int ks = 0; ks < 16; ks++) {
+                const uint32_t row = mt * 16u + (lane & 7u) + 8u * ((lane >> 3) & 1u);
+                const uint32_t chunk = 2u * ks + (lane >> 4);
+                const uint32_t pc = (chunk & ~7u) | ((chunk ^ row) & 7u);
+                ldmatrix_x4(qf[mt][ks], qs + row * 512u + pc * 16u);
+            }
+    }
+
+    float o[2][4][4];
+#pragma unroll
+    for (int a = 0; a < 2; a++)
+#pragma unroll
+        for (int b = 0; b < 4; b++)
+#pragma unroll
+            for (int c = 0; c < 4; c++) o[a][b][c] = 0.0f;
+
+    // softmax ownership: 8 threads per row
+    const uint32_t srow = tid >> 3, seg = tid & 7u;
+    const uint32_t stok = srow >> 3;
+    const uint32_t vis = min(it.pos + 1u + stok, it.key_hi);
+    const uint32_t klo = max(it.first_pos, it.key_lo);
+    float m_run = NEG_BIG, l_run = 0.0f;
+    float *S = reinterpret_cast<float *>(smem + V16_OFF_S);
+    float *cfs = reinterpret_cast<float *>(smem + V16_OFF_CF);
+    const uint32_t Pbase = smem_base + V16_OFF_P;
+    bool aborted = false;
+    const uint32_t g = lane >> 2, qd = lane & 3u;
+
+    for (uint32_t j = 0; j < nt; j++) {
+        const uint32_t s = j % V16_NST;
+        if (!aborted && !mbar_wait_bounded(bar0 + 8u * s, (j / V16_NST) & 1u, WAIT_LIMIT)) {
+            aborted = true;
+            atomicOr(status, DEV_ERR_WAIT_TIMEOUT);
+        }
+        const uint32_t Kb = smem_base + s * V16_STAGE, Vb = Kb + 4 * V16_SUB;
+
+        // ---- S = Q K^T for keys 8 warp .. 8 warp + 7 ----
+        float sc[2][4];
+#pragma unroll
+        for (int a = 0; a < 2; a++)
+#pragma unroll
+            for (int c = 0; c < 4; c++) sc[a][c] = 0.0f;
+        {
+            const uint32_t krow = warp * 8u + (lane & 7u);
+            const uint32_t jm = lane >> 3; // which 8x8 matrix this lane addresses
+#pragma unroll
+            for (int kp = 0; kp < 8; kp++) { // 32 dims per step
+                uint32_t kb[4];
+                ldmatrix_x4(kb, Kb + (kp >> 1) * V16_SUB + swz128(krow, (kp & 1) * 4u + jm));
+                mma_f16(sc[0], qf[0][2 * kp], kb[0], kb[1]);
+                mma_f16(sc[1], qf[1][2 * kp], kb[0], kb[1]);
+                mma_f16(sc[0], qf[0][2 * kp + 1], kb[2], kb[3]);
+                mma_f16(sc[1], qf[1][2 * kp + 1], kb[2], kb[3]);
+            }
+        }
+#pragma unroll
+        for (int mt = 0; mt < 2; mt++) {
+            float *r0 = S + (mt * 16u + g) * V16_S_STRIDE + warp * 8u + 2u * qd;
+            *reinterpret_cast<float2 *>(r0) = make_float2(sc[mt][0], sc[mt][1]);
+            *reinterpret_cast<float2 *>(r0 + 8 * V16_S_STRIDE) = make_float2(sc[mt][2], sc[mt][3]);
+        }
+        __syncthreads(); // S complete; every warp is past the P V of the previous tile
+
+        if (tid == 0 && j >= 1 && j - 1 + V16_NST < nt) issue(j - 1 + V16_NST); // refill the stage just released
+
+        // ---- softmax of row srow over this tile's 64 keys ----
+        {
+            const float4 a = *reinterpret_cast<const float4 *>(S + srow * V16_S_STRIDE + seg * 8u);
+            const float4 b = *reinterpret_cast<const float4 *>(S + srow * V16_S_STRIDE + seg * 8u + 4u);
+            float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+            const uint32_t key0 = (t0 + j) * TILE + seg * 8u;
+            float mt_ = NEG_BIG;
+#pragma unroll
+            for (int c = 0; c < 8; c++) {
+                const uint32_t key = key0 + c;
+                v[c] = (key >= klo && key < vis) ? v[c] * SCALE : NEG_BIG; // scale, then mask (M/dmx.rs:71)
+                mt_ = fmaxf(mt_, v[c]);
+            }
+            mt_ = fmaxf(mt_, __shfl_xor_sync(0xffffffffu, mt_, 1));
+            mt_ = fmaxf(mt_, __shfl_xor_sync(0xffffffffu, mt_, 2));
+            mt_ = fmaxf(mt_, __shfl_xor_sync(0xffffffffu, mt_, 4));
+            const float m_new = fmaxf(m_run, mt_);
+            float sum = 0.0f;
+            uint32_t pk[4];
+#pragma unroll
+            for (int c = 0; c < 8; c += 2) {
+                const float w0 = v[c] > NEG_TEST ? __expf(v[c] - m_new) : 0.0f;
+                const float w1 = v[c + 1] > NEG_TEST ? __expf(v[c + 1] - m_new) : 0.0f;
+                const __half2 h = __floats2half2_rn(w0, w1);
+                const float2 f = __half22float2(h);
+                sum += f.x + f.y;
+                pk[c >> 1] = *reinterpret_cast<const uint32_t *>(&h);
+            }
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+            const float cf = m_run > NEG_TEST ? __expf(m_run - m_new) : 0.0f;
+            l_run = l_run * cf + sum;
+            m_run = m_new;
+            *reinterpret_cast<uint4 *>(smem + V16_OFF_P + swz128(srow, seg)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            if (seg == 0) cfs[srow] = cf;
+        }
+        __syncthreads(); // P and the rescale factors are visible
+
+        // ---- O = O * cf + P V for dims 32 warp .. 32 warp + 31 ----
+        {
+            const float c0 = cfs[g], c1 = cfs[g + 8], c2 = cfs[16 + g], c3 = cfs[24 + g];
+#pragma unroll
+            for (int n = 0; n < 4; n++) {
+                o[0][n][0] *= c0; o[0][n][1] *= c0; o[0][n][2] *= c1; o[0][n][3] *= c1;
+                o[1][n][0] *= c2; o[1][n][1] *= c2; o[1][n][2] *= c3; o[1][n][3] *= c3;
+            }
+            const uint32_t Vsub = Vb + (warp >> 1) * V16_SUB;
+            const uint32_t cb = (warp & 1u) * 4u;
+            const uint32_t jm = lane >> 3;
+#pragma unroll
+            for (int ks = 0; ks < 4; ks++) { // 16 keys per step
+                uint32_t pa[2][4];
+#pragma unroll
+                for (int mt = 0; mt < 2; mt++) {
+                    const uint32_t row = mt * 16u + (lane & 7u) + 8u * ((lane >> 3) & 1u);
+                    ldmatrix_x4(pa[mt], Pbase + swz128(row, 2u * ks + (lane >> 4)));
+                }
+#pragma unroll
+                for (int np = 0; np < 2; np++) { // two 8-dim tiles per load
+                    uint32_t vb[4];
+                    const uint32_t key = 16u * ks + (lane & 7u) + 8u * (jm & 1u);
+                    ldmatrix_x4_trans(vb, Vsub + swz128(key, cb + 2u * np + (jm >> 1)));
+                    mma_f16(o[0][2 * np], pa[0], vb[0], vb[1]);
+                    mma_f16(o[1][2 * np], pa[1], vb[0], vb[1]);
+                    mma_f16(o[0][2 * np + 1], pa[0], vb[2], vb[3]);
+                    mma_f16(o[1][2 * np + 1], pa[1], vb[2], vb[3]);
+                }
+            }
+        }
+    }
+
+    // ---- the piece's partial: [m, l] per row and O[32][256] ----
+    const size_t piece = (size_t)kvh * it.nsplit + split;
+    if (seg == 0) {
+        float2 *ml = reinterpret_cast<float2 *>(it.part_ml) + piece * 32u + srow;
+        *ml = make_float2(m_run, l_run);
+    }
+    {
+        float *po = it.part_o + piece * 32u * 256u;
+#pragma unroll
+        for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+            for (int n = 0; n < 4; n++) {
+                const uint32_t row = mt * 16u + g, col = warp * 32u + n * 8u + 2u * qd;
+                *reinterpret_cast<float2 *>(po + (size_t)row * 256u + col) = make_float2(o[mt][n][0], o[mt][n][1]);
+                *reinterpret_cast<float2 *>(po + (size_t)(row + 8u) * 256u + col) = make_float2(o[mt][n][2], o[mt][n][3]);
+            }
+    }
+}
+
+// Log-sum-exp merge of the pieces of one row: attn_fd_combine's arithmetic (W/ops.wgsl:529-537) over this
+// library's pieces. grid = (64 rows, items); thread = dim. In partial mode the merged, un-normalised record
+// [M, tot, acc[256]] is written instead (row = tok * 16 + head), for the merge across sequence shards.
+__global__ void __launch_bounds__(256)
+combine_kernel(const VerifyItem *__restrict__ items, const __grid_constant__ VerifyItem single) {
+    const VerifyItem &it = items ? items[blockIdx.y] : single;
+    const uint32_t r = blockIdx.x; // kvh * 32 + row
+    const uint32_t kvh = r >> 5, row = r & 31u, tok = row >> 3, head = 8u * kvh + (row & 7u);
+    if (tok >= it.ntok) {
+        if (it.partial) { // rows of tokens beyond the step: the empty record
+            float *rec = it.out + (size_t)(tok * 16u + head) * REC;
+            rec[2 + threadIdx.x] = 0.0f;
+            if (threadIdx.x == 0) {
+                rec[0] = NEG_BIG;
+                rec[1] = 0.0f;
+            }
+        }
+        return;
+    }
+    __shared__ float e_s[MAX_SPLITS];
+    __shared__ float red[8];
+    __shared__ float tot_s, M_s;
+    const uint32_t ns = it.nsplit, tid = threadIdx.x;
+    const float2 *ml = reinterpret_cast<const float2 *>(it.part_ml) + (size_t)kvh * ns * 32u + row;
+    float m = NEG_BIG, l = 0.0f;
+    if (tid < ns) {
+        const float2 x = ml[(size_t)tid * 32u];
+        m = x.x;
+        l = x.y;
+    }
+    float M = m;
+#pragma unroll
+    for (int sh = 16; sh > 0; sh >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, sh));
+    if ((tid & 31u) == 0) red[tid >> 5] = M;
+    __syncthreads();
+    if (tid == 0) {
+        float x = red[0];
+        for (int i = 1; i < 8; i++) x = fmaxf(x, red[i]);
+        M_s = x;
+    }
+    __syncthreads();
+    M = M_s;
+    const float e = tid < ns ? expf(m - M) : 0.0f;
+    if (tid < ns) e_s[tid] = e;
+    float t = e * l;
+#pragma unroll
+    for (int sh = 16; sh > 0; sh >>= 1) t += __shfl_xor_sync(0xffffffffu, t, sh);
+    __syncthreads(); // red is free again
+    if ((tid & 31u) == 0) red[tid >> 5] = t;
+    __syncthreads();
+    if (tid == 0) {
+        float x = 0.0f;
+        for (int i = 0; i < 8; i++) x += red[i];
+        tot_s = x;
+    }
+    __syncthreads();
+    const float tot = tot_s;
+    const float *po = it.part_o + ((size_t)kvh * ns * 32u + row) * 256u + tid;
+    float acc0 = 0.0f, acc1 = 0.0f, acc2 = 0.0f, acc3 = 0.0f;
+    uint32_t s = 0;
+    for (; s + 4 <= ns; s += 4) {
+        const float x0 = po[(size_t)(s + 0) * 8192u], x1 = po[(size_t)(s + 1) * 8192u];
+        const float x2 = po[(size_t)(s + 2) * 8192u], x3 = po[(size_t)(s + 3) * 8192u];
+        acc0 += e_s[s] * x0;
+        acc1 += e_s[s + 1] * x1;
+        acc2 += e_s[s + 2] * x2;
+        acc3 += e_s[s + 3] * x3;
+    }
+    for (; s < ns; s++) acc0 += e_s[s] * po[(size_t)s * 8192u];
+    const float acc = (acc0 + acc1) + (acc2 + acc3);
+    if (it.partial) {
+        float *rec = it.out + (size_t)(tok * 16u + head) * REC;
+        rec[2 + tid] = acc;
+        if (tid == 0) {
+            rec[0] = M;
+            rec[1] = tot;
+        }
+    } else {
+        it.out[(size_t)tok * 4096u + (size_t)head * 256u + tid] = acc / tot;
+    }
+}
+
+// Merge of the records of n sequence shards (W/ops.wgsl:529-537 with shards in place of blocks):
+// recs = [n_shards][64][258]; grid = 16 * ntok rows; thread = dim.
+__global__ void __launch_bounds__(256)
+combine_shards_kernel(const float *__restrict__ recs, int n_shards, float *__restrict__ out) {
+    const uint32_t r = blockIdx.x, d = threadIdx.x;
+    float M = NEG_BIG;
+    for (int g = 0; g < n_shards; g++) M = fmaxf(M, recs[((size_t)g * 64u + r) * REC]);
+    float tot = 0.0f, acc = 0.0f;
+    for (int g = 0; g < n_shards; g++) {
+        const float *x = recs + ((size_t)g * 64u + r) * REC;
+        const float e = expf(x[0] - M);
+        tot += e * x[1];
+        acc += e * x[2 + d];
+    }
+    out[(size_t)r * 256u + d] = acc / tot;
+}
+
+mkv_status launch_combine_shards(Ctx *ctx, const float *recs, int n_shards, uint32_t ntok, float *out) {
+    combine_shards_kernel<<<16u * ntok, 256, 0, ctx->stream>>>(recs, n_shards, out);
+    ctx->launches++;
+    MKV_CUDA(cudaGetLastError());
+    return MKV_OK;
+}
+
+mkv_status launch_verify_f32(Ctx *ctx, const VerifyItem *items_dev, int n, const VerifyItem &single, uint32_t total_ctas);
+mkv_status verify_f32_setup_device();
+
+// dynamic shared memory opt-in for the current device (once per context creation)
+mkv_status verify_setup_device() {
+    MKV_CUDA(cudaFuncSetAttribute(verify_f16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)V16_SMEM));
+    return verify_f32_setup_device();
+}
+
+mkv_status launch_verify(Ctx *ctx, mkv_fmt fmt, const VerifyItem *items_host, int n, bool batch) {
+    uint32_t total = 0;
+    for (int i = 0; i < n; i++) total += 2u * items_host[i].nsplit;
+    const VerifyItem *items_dev = nullptr;
+    int slot = -1;
+    if (batch) {
+        if (n > Ctx::SLOT_ITEMS) {
+            set_error("verify batch of %d items exceeds %d", n, Ctx::SLOT_ITEMS);
+            return MKV_ERR_INVALID;
+        }
+        // next staging slot; wait for the copy that last used it
+        slot = ctx->slot_next;
+        ctx->slot_next = (slot + 1) % Ctx::SLOTS;
+        if (ctx->slot_used[slot]) MKV_CUDA(cudaEventSynchronize(ctx->slot_done[slot]));
+        VerifyItem *h = ctx->items_host + (size_t)slot * Ctx::SLOT_ITEMS;
+        VerifyItem *d = ctx->items_dev + (size_t)slot * Ctx::SLOT_ITEMS;
+        memcpy(h, items_host, sizeof(VerifyItem) * (size_t)n);
+        MKV_CUDA(cudaMemcpyAsync(d, h, sizeof(VerifyItem) * (size_t)n, cudaMemcpyHostToDevice, ctx->stream));
+        MKV_CUDA(cudaEventRecord(ctx->slot_done[slot], ctx->stream));
+        ctx->slot_used[slot] = true;
+        items_dev = d;
+    }
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    if (ctx->prof) {
+        if (ctx->prof_used == ctx->prof_events.size()) {
+            cudaEvent_t a, b;
+            MKV_CUDA(cudaEventCreate(&a));
+            MKV_CUDA(cudaEventCreate(&b));
+            ctx->prof_events.push_back({a, b});
+        }
+        e0 = ctx->prof_events[ctx->prof_used].first;
+        e1 = ctx->prof_events[ctx->prof_used].second;
+        ctx->prof_used++;
+        MKV_CUDA(cudaEventRecord(e0, ctx->stream));
+    }
+    if (total > 0) {
+        if (fmt == MKV_F16) {
+            verify_f16_kernel<<<total, 256, V16_SMEM, ctx->stream>>>(items_dev, n, items_host[0], ctx->dev_status);
+            ctx->launches++;
+            MKV_CUDA(cudaGetLastError());
+        } else {
+            mkv_status st = launch_verify_f32(ctx, items_dev, n, items_host[0], total);
+            if (st != MKV_OK) return st;
+        }
+    }
+    if (ctx->prof) MKV_CUDA(cudaEventRecord(e1, ctx->stream));
+    combine_kernel<<<dim3(64, (unsigned)n), 256, 0, ctx->stream>>>(items_dev, items_host[0]);
+    ctx->launches++;
+    MKV_CUDA(cudaGetLastError());
+    return MKV_OK;
+}
+
+// Chooses tiles_per_split so that all items together fill the SMs in one wave (one CTA per SM), and lays
+// the items out in the flattened grid. Items must have tile_begin / tile_end set.
+void plan_items(Ctx *ctx, VerifyItem *items, int n) {
+    uint64_t tiles = 0;
+    uint32_t min_tps = 1;
+    for (int i = 0; i < n; i++) {
+        const uint32_t t = items[i].tile_end - items[i].tile_begin;
+        tiles += 2ull * t;
+        const uint32_t need = (t + MAX_SPLITS - 1) / MAX_SPLITS;
+        if (need > min_tps) min_tps = need;
+    }
+    const uint32_t budget = (uint32_t)ctx->sm_count;
+    uint32_t tps = (uint32_t)((tiles + budget - 1) / budget);
+    if (tps < min_tps) tps = min_tps;
+    for (;; tps++) {
+        uint64_t ctas = 0;
+        for (int i = 0; i < n; i++) ctas += 2ull * ((items[i].tile_end - items[i].tile_begin + tps - 1) / tps);
+        if (ctas <= budget || ctas <= 2ull * (uint64_t)n) break; // one wave, or nothing left to merge
+    }
+    uint32_t cta = 0;
+    for (int i = 0; i < n; i++) {
+        const uint32_t t = items[i].tile_end - items[i].tile_begin;
+        items[i].tiles_per_split = tps;
+        items[i].nsplit = (t + tps - 1) / tps;
+        items[i].cta_begin = cta;
+        cta += 2u * items[i].nsplit;
+    }
+}
+
+} // namespace mkv
