@@ -9,7 +9,7 @@
  * Conventions
  *  - Every call returns an mkv_status; nothing aborts. mkv_last_error() gives the text of the last failure
  *    on the calling thread.
- *  - One mkv_ctx = one CUDA device + one compute stream (+ one copy stream). Calls on a ctx come from one
+ *  - One mkv_ctx = one CUDA device + the caller's compute stream (+ a copy stream of its own). Calls on a ctx come from one
  *    host thread at a time (the reference engine is single-threaded, engine/crates/api/src/lib.rs:46) and are
  *    stream-ordered: they return once the work is enqueued, except where "blocks" is written.
  *  - Pointers named *_dev are device pointers on the ctx's device, borrowed for the call; *_host are host
@@ -61,7 +61,7 @@ const char *mkv_version(void);
 
 /* ---- context ------------------------------------------------------------------------------------------
  * Replaces gpu::Gpu's device/queue for this path (engine/crates/gpu/src/lib.rs:60-139). `stream` is a
- * cudaStream_t to run on (borrowed; e.g. the caller's current stream) or NULL for a stream the ctx creates. */
+ * cudaStream_t to run on (borrowed; e.g. the caller's current stream); NULL is the legacy default stream. */
 mkv_status mkv_ctx_create(int device, void *stream, mkv_ctx **out);
 void mkv_ctx_destroy(mkv_ctx *ctx);
 /* blocks until everything enqueued on both streams has finished */

@@ -254,12 +254,7 @@ mkv_status mkv_ctx_create(int device, void *stream, mkv_ctx **out) {
     if (!ctx) return MKV_ERR_NOMEM;
     ctx->device = device;
     ctx->sm_count = prop.multiProcessorCount;
-    if (stream) {
-        ctx->stream = (cudaStream_t)stream;
-    } else {
-        MKV_CUDA(cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking));
-        ctx->own_stream = true;
-    }
+    ctx->stream = (cudaStream_t)stream; // NULL = the legacy default stream
     MKV_CUDA(cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking));
     MKV_CUDA(cudaEventCreateWithFlags(&ctx->ev_compute, cudaEventDisableTiming));
     MKV_CUDA(cudaEventCreateWithFlags(&ctx->ev_copy, cudaEventDisableTiming));

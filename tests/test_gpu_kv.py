@@ -1,0 +1,509 @@
+"""Parity of the CUDA path (through the C ABI) against the CPU oracle. Needs a B200.
+
+Bars: append / truncate / snapshot bit-exact; attention max|a-b|/max|b| <= 2e-3 on the f16 cache and <= 1e-5 on
+the f32 cache (the reference's error metric, engine/reference/strato/README.md:6).
+"""
+import numpy as np
+import pytest
+import torch
+
+from mechta_b200 import _lib, kv, synth
+
+pytestmark = pytest.mark.gpu
+
+TOL = {kv.KvFormat.F16: 2e-3, kv.KvFormat.F32: 1e-5}
+FMTS = [kv.KvFormat.F16, kv.KvFormat.F32]
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    assert torch.cuda.is_available(), "these tests need the GPU"
+    torch.cuda.set_device(0)
+    c = kv.KvContext(0, torch.cuda.current_stream())
+    yield c
+    c.close()
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def host_bits(cache, layer):
+    """K and V of a layer as the oracle's arrays (f16 bit patterns or f32)."""
+    k, v = cache.buffer_tensors(layer)
+    torch.cuda.synchronize()
+    if cache.fmt == kv.KvFormat.F16:
+        return k.view(torch.int16).cpu().numpy().view(np.uint16), v.view(torch.int16).cpu().numpy().view(np.uint16)
+    return k.cpu().numpy(), v.cpu().numpy()
+
+
+def fill_both(oracle, cache, layer, rows, seed, first=0, chunk=2048):
+    """Appends `rows` seeded rows from `first` to the device cache and to fresh oracle arrays."""
+    fmt = int(cache.fmt)
+    kc, vc = oracle.new_cache(fmt, cache.capacity), oracle.new_cache(fmt, cache.capacity)
+    for p in range(first, first + rows, chunk):
+        n = min(chunk, first + rows - p)
+        k = synth.normal(seed, synth.S_K, p, (n, 2, 256))
+        v = synth.normal(seed, synth.S_V, p, (n, 2, 256))
+        tab = kv.rope_table(p, n)
+        cache.append(layer, p, dev(k), dev(v), dev(tab))
+        oracle.append(fmt, kc, vc, p, k, v, tab)
+    return kc, vc
+
+
+# ---------------------------------------------------------------- append / rollback ----------------------------
+
+@pytest.mark.parametrize("fmt", FMTS)
+@pytest.mark.parametrize("ntok", [1, 2, 3, 4, 64, 2048])
+def test_append_bit_exact(ctx, oracle, fmt, ntok):
+    cache = kv.KvCache(ctx, fmt, 2, 4096)
+    pos = 4096 - ntok if ntok > 4 else 1029
+    k = synth.normal(21, synth.S_KNEW, ntok, (ntok, 2, 256)) * 4.0
+    v = synth.normal(21, synth.S_VNEW, ntok, (ntok, 2, 256)) * 4.0
+    k[0, 0, :6] = [70000.0, -70000.0, 1e-7, 6e-8, 2.0**-24, 65519.0]  # overflow, subnormals, ties
+    tab = kv.rope_table(pos, ntok)
+    cache.append(1, pos, dev(k), dev(v), dev(tab))
+    kc, vc = oracle.new_cache(int(fmt), 4096), oracle.new_cache(int(fmt), 4096)
+    oracle.append(int(fmt), kc, vc, pos, k, v, tab)
+    gk, gv = host_bits(cache, 1)
+    assert np.array_equal(gk, kc) and np.array_equal(gv, vc)
+    assert len(cache) == pos + ntok
+    zk, zv = host_bits(cache, 0)  # the other layer is untouched and zero-initialised
+    assert not zk.any() and not zv.any()
+    cache.close()
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+def test_append_without_table_and_all_layers(ctx, oracle, fmt):
+    n_layers, ntok, pos = 3, 4, 200
+    cache = kv.KvCache(ctx, fmt, n_layers, 4096)
+    k = synth.normal(22, synth.S_KNEW, 0, (n_layers, ntok, 2, 256))
+    v = synth.normal(22, synth.S_VNEW, 0, (n_layers, ntok, 2, 256))
+    tab = kv.rope_table(pos, ntok)
+    cache.append_layers(pos, dev(k), dev(v), dev(tab))
+    for l in range(n_layers):
+        kc, vc = oracle.new_cache(int(fmt), 4096), oracle.new_cache(int(fmt), 4096)
+        oracle.append(int(fmt), kc, vc, pos, k[l], v[l], tab)
+        gk, gv = host_bits(cache, l)
+        assert np.array_equal(gk, kc) and np.array_equal(gv, vc)
+    cache.append(0, pos, dev(k[0]), dev(v[0]), None)  # K already rotated
+    kc, vc = oracle.new_cache(int(fmt), 4096), oracle.new_cache(int(fmt), 4096)
+    oracle.append(int(fmt), kc, vc, pos, k[0], v[0], None)
+    gk, _ = host_bits(cache, 0)
+    assert np.array_equal(gk, kc)
+    cache.close()
+
+
+def test_capacity_and_argument_errors(ctx):
+    for bad in (4000, 1024, 262144 + 1024):
+        with pytest.raises(_lib.MkvError) as e:
+            kv.KvCache(ctx, kv.KvFormat.F16, 1, bad)
+        assert e.value.status == _lib.ERR_INVALID
+    cache = kv.KvCache(ctx, kv.KvFormat.F16, 1, 4096)
+    k = torch.zeros(4, 2, 256, device="cuda")
+    with pytest.raises(_lib.MkvError) as e:
+        cache.append(0, 4093, k, k, None)  # rows 4093..4096 do not fit
+    assert e.value.status == _lib.ERR_CAPACITY
+    with pytest.raises(_lib.MkvError) as e:
+        cache.append(1, 0, k, k, None)
+    assert e.value.status == _lib.ERR_INVALID
+    q = torch.zeros(4, 16, 256, device="cuda")
+    out = torch.empty_like(q)
+    with pytest.raises(_lib.MkvError) as e:
+        cache.attn_verify(0, 0, 10, q, out)  # nothing appended yet
+    assert e.value.status == _lib.ERR_STATE
+    cache.append(0, 0, k, k, None)
+    with pytest.raises(_lib.MkvError) as e:
+        cache.attn_verify(0, 0, 0, torch.zeros(5, 16, 256, device="cuda"), torch.zeros(5, 16, 256, device="cuda"))
+    assert e.value.status == _lib.ERR_INVALID
+    with pytest.raises(_lib.MkvError) as e:
+        cache.truncate(9)
+    assert e.value.status == _lib.ERR_STATE
+    cache.close()
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+def test_truncate_rollback(ctx, oracle, fmt):
+    """Rows [0, new_len) unchanged and visible; rows beyond never observed; scrub zeroes them."""
+    cache = kv.KvCache(ctx, fmt, 1, 4096)
+    pos = 500
+    kc, vc = fill_both(oracle, cache, 0, pos + 4, 23)
+    q = synth.normal(23, synth.S_Q, 0, (4, 16, 256))
+    qd, out = dev(q), torch.empty(4, 16, 256, device="cuda")
+    before = host_bits(cache, 0)
+    cache.truncate(pos + 2)  # 1 draft accepted, 2 refused
+    assert len(cache) == pos + 2
+    after = host_bits(cache, 0)
+    assert np.array_equal(before[0], after[0]) and np.array_equal(before[1], after[1])  # refused rows stay in memory
+    with pytest.raises(_lib.MkvError) as e:
+        cache.attn_verify(0, 0, pos, qd, out)  # would read the refused rows
+    assert e.value.status == _lib.ERR_STATE
+    # the next step starts at the new length and overwrites them
+    k2 = synth.normal(24, synth.S_KNEW, 0, (4, 2, 256))
+    v2 = synth.normal(24, synth.S_VNEW, 0, (4, 2, 256))
+    tab = kv.rope_table(pos + 2, 4)
+    cache.append(0, pos + 2, dev(k2), dev(v2), dev(tab))
+    oracle.append(int(fmt), kc, vc, pos + 2, k2, v2, tab)
+    cache.attn_verify(0, 0, pos + 2, qd, out)
+    want = oracle.attn_ref_f32(int(fmt), kc, vc, 0, pos + 2, q)
+    assert oracle.max_rel(out.cpu().numpy(), want) < TOL[fmt]
+    cache.truncate(pos + 3, scrub=True)
+    gk, gv = host_bits(cache, 0)
+    assert np.array_equal(gk[:pos + 3], kc[:pos + 3]) and not gk[pos + 3:].any() and not gv[pos + 3:].any()
+    cache.close()
+
+
+# ---------------------------------------------------------------- verify attention ------------------------------
+
+@pytest.mark.parametrize("fmt", FMTS)
+def test_config0_verify_step(ctx, oracle, fmt):
+    """4,096 prior tokens, append 4, causal verify, roll back 3 (the CPU-runnable configuration)."""
+    cache = kv.KvCache(ctx, fmt, 1, 8192)
+    pos = 4096
+    kc, vc = fill_both(oracle, cache, 0, pos, 31)
+    k = synth.normal(31, synth.S_KNEW, 0, (4, 2, 256))
+    v = synth.normal(31, synth.S_VNEW, 0, (4, 2, 256))
+    q = synth.normal(31, synth.S_Q, 0, (4, 16, 256))
+    tab = kv.rope_table(pos, 4)
+    cache.append(0, pos, dev(k), dev(v), dev(tab))
+    oracle.append(int(fmt), kc, vc, pos, k, v, tab)
+    out = torch.empty(4, 16, 256, device="cuda")
+    cache.attn_verify(0, 0, pos, dev(q), out)
+    cache.truncate(pos + 1)
+    ctx.sync()
+    gk, gv = host_bits(cache, 0)
+    assert np.array_equal(gk, kc) and np.array_equal(gv, vc)
+    want = oracle.attn_ref_f32(int(fmt), kc, vc, 0, pos, q)
+    err = oracle.max_rel(out.cpu().numpy(), want)
+    assert err < TOL[fmt], err
+    assert len(cache) == pos + 1
+    cache.close()
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+@pytest.mark.parametrize("pos,ntok,first", [(0, 1, 0), (0, 4, 0), (3, 4, 0), (59, 4, 0), (60, 4, 0), (61, 4, 0), (63, 2, 0),
+                                            (64, 4, 0), (127, 3, 0), (1000, 4, 0), (1000, 1, 0), (1000, 2, 1), (1000, 4, 333),
+                                            (2047, 4, 2040), (4091, 4, 0), (4092, 4, 64)])
+def test_verify_edges(ctx, oracle, fmt, pos, ntok, first):
+    """Empty prefix, ragged tails around tile edges, windows (the MTP layer's first_pos), end of capacity."""
+    cache = kv.KvCache(ctx, fmt, 1, 4096)
+    kc, vc = fill_both(oracle, cache, 0, pos + ntok, 41 + pos)
+    q = synth.normal(41, synth.S_Q, pos, (ntok, 16, 256))
+    out = torch.full((ntok, 16, 256), float("nan"), device="cuda")
+    cache.attn_verify(0, first, pos, dev(q), out)
+    ctx.sync()
+    want = oracle.attn_ref_f32(int(fmt), kc, vc, first, pos, q)
+    got = out.cpu().numpy()
+    assert np.isfinite(got).all()
+    err = oracle.max_rel(got, want)
+    assert err < TOL[fmt], err
+    cache.close()
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+def test_stale_rows_beyond_the_length_do_not_leak(ctx, oracle, fmt):
+    """The tail tile reads rows past the visible range; whatever they hold must not change the result."""
+    cache = kv.KvCache(ctx, fmt, 1, 4096)
+    pos = 700
+    kc, vc = fill_both(oracle, cache, 0, pos + 64, 43)  # 60 rows of 'refused drafts' beyond the step
+    cache.truncate(pos)
+    k = synth.normal(43, synth.S_KNEW, 0, (4, 2, 256))
+    v = synth.normal(43, synth.S_VNEW, 0, (4, 2, 256))
+    q = synth.normal(43, synth.S_Q, 0, (4, 16, 256))
+    tab = kv.rope_table(pos, 4)
+    cache.append(0, pos, dev(k), dev(v), dev(tab))
+    oracle.append(int(fmt), kc, vc, pos, k, v, tab)
+    out = torch.empty(4, 16, 256, device="cuda")
+    cache.attn_verify(0, 0, pos, dev(q), out)
+    want = oracle.attn_ref_f32(int(fmt), kc, vc, 0, pos, q)
+    assert oracle.max_rel(out.cpu().numpy(), want) < TOL[fmt]
+    cache.close()
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+def test_verify_is_deterministic(ctx, oracle, fmt):
+    cache = kv.KvCache(ctx, fmt, 1, 8192)
+    pos = 5000
+    fill_both(oracle, cache, 0, pos + 4, 45)
+    q = dev(synth.normal(45, synth.S_Q, 0, (4, 16, 256)))
+    a, b = torch.empty(4, 16, 256, device="cuda"), torch.empty(4, 16, 256, device="cuda")
+    cache.attn_verify(0, 0, pos, q, a)
+    cache.attn_verify(0, 0, pos, q, b)
+    ctx.sync()
+    assert torch.equal(a, b)
+    cache.close()
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+def test_steady_state_steps_with_random_accepts(ctx, oracle, fmt):
+    """The loop of the steady-state configuration, short: append 4, verify, accept 0..3, roll back the rest."""
+    n_layers, steps, pos = 2, 12, 1500
+    cache = kv.KvCache(ctx, fmt, n_layers, 4096)
+    ocs = [fill_both(oracle, cache, l, pos, 50 + l) for l in range(n_layers)]
+    acc = synth.accept_counts(51, steps)
+    out = torch.empty(4, 16, 256, device="cuda")
+    for s in range(steps):
+        k = synth.normal(52, synth.S_KNEW, s, (n_layers, 4, 2, 256))
+        v = synth.normal(52, synth.S_VNEW, s, (n_layers, 4, 2, 256))
+        q = synth.normal(52, synth.S_Q, s, (n_layers, 4, 16, 256))
+        tab = kv.rope_table(pos, 4)
+        cache.append_layers(pos, dev(k), dev(v), dev(tab))
+        for l in range(n_layers):
+            oracle.append(int(fmt), ocs[l][0], ocs[l][1], pos, k[l], v[l], tab)
+            cache.attn_verify(l, 0, pos, dev(q[l]), out)
+            want = oracle.attn_ref_f32(int(fmt), ocs[l][0], ocs[l][1], 0, pos, q[l])
+            assert oracle.max_rel(out.cpu().numpy(), want) < TOL[fmt]
+        pos += 1 + int(acc[s])
+        cache.truncate(pos)
+    for l in range(n_layers):
+        gk, gv = host_bits(cache, l)
+        assert np.array_equal(gk[:pos], ocs[l][0][:pos]) and np.array_equal(gv[:pos], ocs[l][1][:pos])
+    cache.close()
+
+
+@pytest.mark.parametrize("fmt,ctx_len", [(kv.KvFormat.F16, 65536), (kv.KvFormat.F32, 32768)])
+def test_verify_full_size_against_oracle(ctx, oracle, fmt, ctx_len):
+    """One layer at the benchmark's context length against the oracle, plus linearity in V."""
+    cache = kv.KvCache(ctx, fmt, 1, ctx_len + 1024)
+    pos = ctx_len
+    kc, vc = fill_both(oracle, cache, 0, pos + 4, 61, chunk=4096)
+    q = synth.normal(61, synth.S_Q, 0, (4, 16, 256))
+    out = torch.empty(4, 16, 256, device="cuda")
+    cache.attn_verify(0, 0, pos, dev(q), out)
+    ctx.sync()
+    want = oracle.attn_ref_f32(int(fmt), kc, vc, 0, pos, q)
+    err = oracle.max_rel(out.cpu().numpy(), want)
+    assert err < TOL[fmt], err
+    # scaling V by 2 (exact in both formats) scales the output by 2 exactly
+    _, v = cache.buffer_tensors(0)
+    v.mul_(2.0)
+    out2 = torch.empty_like(out)
+    cache.attn_verify(0, 0, pos, dev(q), out2)
+    ctx.sync()
+    assert torch.equal(out2, out * 2.0)
+    cache.close()
+
+
+# ---------------------------------------------------------------- shards and batches ----------------------------
+
+@pytest.mark.parametrize("fmt", FMTS)
+@pytest.mark.parametrize("n_shards", [2, 4, 8])
+def test_sequence_shards_on_one_gpu(ctx, oracle, fmt, n_shards):
+    """Each shard holds a contiguous range; records merged by combine_shards equal the unsharded result."""
+    total, pos, ntok = 8192, 8192 - 4, 4
+    per = total // n_shards
+    whole = kv.KvCache(ctx, fmt, 1, total)
+    kc, vc = fill_both(oracle, whole, 0, total, 71)
+    shards = [kv.KvCache(ctx, fmt, 1, per, shard_first=g * per) for g in range(n_shards)]
+    for p in range(0, total, 2048):  # every shard sees every append and keeps its own rows
+        k = dev(synth.normal(71, synth.S_K, p, (2048, 2, 256)))
+        v = dev(synth.normal(71, synth.S_V, p, (2048, 2, 256)))
+        tab = dev(kv.rope_table(p, 2048))
+        for s in shards:
+            s.append(0, p, k, v, tab)
+    hk, hv = host_bits(whole, 0)
+    for g, s in enumerate(shards):
+        gk, gv = host_bits(s, 0)
+        assert np.array_equal(gk, hk[g * per:(g + 1) * per]) and np.array_equal(gv, hv[g * per:(g + 1) * per])
+    q = synth.normal(71, synth.S_Q, 0, (ntok, 16, 256))
+    recs = torch.empty(n_shards, 64, 258, device="cuda")
+    for g, s in enumerate(shards):
+        s.attn_verify_partial(0, 0, pos, dev(q), recs[g])
+    out = torch.empty(ntok, 16, 256, device="cuda")
+    ctx.combine_shards(recs, ntok, out)
+    ctx.sync()
+    want = oracle.attn_ref_f32(int(fmt), kc, vc, 0, pos, q)
+    assert oracle.max_rel(out.cpu().numpy(), want) < TOL[fmt]
+    # each record against the oracle's shard record (same un-normalised format)
+    r = recs.cpu().numpy()
+    for g in range(n_shards):
+        wr = oracle.attn_shard_partial(int(fmt), kc[g * per:], vc[g * per:], g * per, g * per, (g + 1) * per, 0, pos, q)
+        e = np.exp(wr[:, 0] - r[g][:, 0])  # the two may use different reference maxima
+        assert np.allclose(r[g][:, 1], wr[:, 1] * e, rtol=TOL[fmt] * 5, atol=0)
+    # a window that starts inside shard 1: shard 0 contributes the empty record
+    first = per + 100
+    for g, s in enumerate(shards):
+        s.attn_verify_partial(0, first, pos, dev(q[:2]), recs[g])
+    ctx.combine_shards(recs, 2, out[:2])
+    ctx.sync()
+    r0 = recs[0].cpu().numpy()
+    assert (r0[:32, 0] == np.float32(-3.0e38)).all() and not r0[:32, 1:].any()
+    want = oracle.attn_ref_f32(int(fmt), kc, vc, first, pos, q[:2])
+    assert oracle.max_rel(out[:2].cpu().numpy(), want) < TOL[fmt]
+    for s in shards:
+        s.close()
+    whole.close()
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+def test_ragged_batch_of_sessions(ctx, oracle, fmt):
+    """Several sessions of different lengths in one launch pair; each equals its own single call."""
+    lens = [64, 1024, 1500, 3000, 4000, 129, 2048]
+    caches, ocs, qs, outs, singles = [], [], [], [], []
+    for i, n in enumerate(lens):
+        c = kv.KvCache(ctx, fmt, 2, 4096)
+        ocs.append(fill_both(oracle, c, 1, n + 4, 80 + i))
+        caches.append(c)
+        ntok = 4 if i % 3 else 2
+        q = synth.normal(80 + i, synth.S_Q, 0, (ntok, 16, 256))
+        qs.append(q)
+        outs.append(torch.empty(ntok, 16, 256, device="cuda"))
+        singles.append(torch.empty(ntok, 16, 256, device="cuda"))
+    dq = [dev(q) for q in qs]
+    ctx.attn_verify_batch([(caches[i], 1, 0, lens[i], dq[i], outs[i]) for i in range(len(lens))])
+    for i in range(len(lens)):
+        caches[i].attn_verify(1, 0, lens[i], dq[i], singles[i])
+    ctx.sync()
+    for i in range(len(lens)):
+        want = oracle.attn_ref_f32(int(fmt), ocs[i][0], ocs[i][1], 0, lens[i], qs[i])
+        assert oracle.max_rel(outs[i].cpu().numpy(), want) < TOL[fmt]
+        assert oracle.max_rel(outs[i].cpu().numpy(), singles[i].cpu().numpy()) < TOL[fmt]
+    for c in caches:
+        c.close()
+
+
+# ---------------------------------------------------------------- prefill ------------------------------------
+
+@pytest.mark.parametrize("fmt", FMTS)
+@pytest.mark.parametrize("prefix,ntok,first", [(0, 64, 0), (0, 17, 0), (100, 8, 0), (1000, 512, 0), (1000, 128, 300),
+                                                (2048, 2048, 0)])
+def test_prefill_over_cache(ctx, oracle, fmt, prefix, ntok, first):
+    """Token T of the block sees [first, prefix + T]; rows are appended first, as the reference does."""
+    cache = kv.KvCache(ctx, fmt, 1, 4096)
+    kc, vc = fill_both(oracle, cache, 0, prefix + ntok, 90 + ntok)
+    q = synth.normal(90, synth.S_Q, ntok, (ntok, 16, 256))
+    out = torch.full((ntok, 16, 256), float("nan"), device="cuda")
+    cache.attn_prefill(0, first, prefix, dev(q), out)
+    ctx.sync()
+    got = out.cpu().numpy()
+    assert np.isfinite(got).all()
+    toks = sorted(set([0, 1, ntok // 2, ntok - 2, ntok - 1]) & set(range(ntok))) if ntok > 64 else list(range(ntok))
+    want = oracle.attn_ref_f32_sel(int(fmt), kc, vc, first, prefix, toks, q)
+    err = oracle.max_rel(got[toks], want)
+    assert err < TOL[fmt], err
+    cache.close()
+
+
+# ---------------------------------------------------------------- snapshot / restore ---------------------------
+
+@pytest.mark.parametrize("fmt", FMTS)
+def test_snapshot_restore_bit_exact(ctx, oracle, fmt, tmp_path):
+    n_layers, rows, p = 3, 1500, 1300
+    a = kv.KvCache(ctx, fmt, n_layers, 4096)
+    ocs = [fill_both(oracle, a, l, rows, 100 + l) for l in range(n_layers)]
+    root = a.read_root(p)
+    want = oracle.snapshot(int(fmt), [o[0] for o in ocs], [o[1] for o in ocs], p)
+    assert root.payload.numel() == a.snapshot_bytes(p) == want.size
+    assert np.array_equal(root.payload.numpy(), want)  # layout: per layer K rows then V rows (engine.rs:790-795)
+    with pytest.raises(_lib.MkvError) as e:
+        a.read_root(rows + 1)
+    assert e.value.status == _lib.ERR_STATE
+    # through a root file into a fresh cache
+    toks = np.arange(p, dtype=np.uint32)
+    path = str(tmp_path / f"root-{fmt.name.lower()}-{kv.root_key(toks)}.bin")
+    kv.write_root_file(path, toks, root)
+    t2, r2 = kv.read_root_file(path, fmt, n_layers)
+    assert np.array_equal(t2, toks)
+    b = kv.KvCache(ctx, fmt, n_layers, 4096)
+    b.write_root(r2)
+    assert len(b) == p
+    for l in range(n_layers):
+        gk, gv = host_bits(b, l)
+        assert np.array_equal(gk[:p], ocs[l][0][:p]) and np.array_equal(gv[:p], ocs[l][1][:p])
+        assert not gk[p:].any() and not gv[p:].any()
+    # continuing at pos = p is indistinguishable from having computed the prefix here
+    k = synth.normal(105, synth.S_KNEW, 0, (4, 2, 256))
+    v = synth.normal(105, synth.S_VNEW, 0, (4, 2, 256))
+    q = dev(synth.normal(105, synth.S_Q, 0, (4, 16, 256)))
+    tab = dev(kv.rope_table(p, 4))
+    oa, ob = torch.empty(4, 16, 256, device="cuda"), torch.empty(4, 16, 256, device="cuda")
+    a.truncate(p)
+    for c, o in ((a, oa), (b, ob)):
+        c.append(2, p, dev(k), dev(v), tab)
+        c.attn_verify(2, 0, p, q, o)
+    ctx.sync()
+    assert torch.equal(oa, ob)
+    with pytest.raises(_lib.MkvError) as e:
+        b.write_root(kv.Root(p, fmt, n_layers, root.payload[:-2]))
+    assert e.value.status == _lib.ERR_FORMAT
+    a.close()
+    b.close()
+
+
+def test_snapshot_of_shards_concatenates_to_the_whole(ctx, oracle):
+    fmt, total, per = kv.KvFormat.F16, 4096, 1024
+    whole = kv.KvCache(ctx, fmt, 1, total)
+    fill_both(oracle, whole, 0, 3000, 110)
+    shards = [kv.KvCache(ctx, fmt, 1, per, shard_first=g * per) for g in range(4)]
+    p = 2500
+    hk, hv = host_bits(whole, 0)
+    for g, s in enumerate(shards):
+        kt, vt = s.buffer_tensors(0)
+        wk, wv = whole.buffer_tensors(0)
+        kt.copy_(wk[g * per:(g + 1) * per])
+        vt.copy_(wv[g * per:(g + 1) * per])
+        s.set_len(min(3000, (g + 1) * per))
+    rows = 0
+    for g, s in enumerate(shards):
+        r = s.read_root(p)
+        n = max(0, min(p, (g + 1) * per) - g * per)
+        assert r.payload.numel() == 2 * n * 512 * 2
+        if n:
+            got = r.payload.numpy().view(np.uint16).reshape(2, n, 2, 256)
+            assert np.array_equal(got[0], hk[g * per:g * per + n]) and np.array_equal(got[1], hv[g * per:g * per + n])
+        rows += n
+    assert rows == p
+    for s in shards:
+        s.close()
+    whole.close()
+
+
+# ---------------------------------------------------------------- the reference's dispatch form ---------------
+
+def test_dispatch_with_reference_uniforms(ctx, oracle):
+    """kv_rope2 / kv_copy / attn_dmx2 with the uniforms of quad.rs:284-286."""
+    import struct
+    fmt = kv.KvFormat.F16
+    cache = kv.KvCache(ctx, fmt, 1, 4096)
+    pos, K = 900, 4
+    kc, vc = fill_both(oracle, cache, 0, pos, 120)
+    k = synth.normal(120, synth.S_KNEW, 0, (K, 2, 256))
+    v = synth.normal(120, synth.S_VNEW, 0, (K, 2, 256))
+    q = synth.normal(120, synth.S_Q, 0, (K, 16, 256))
+    tab = kv.rope_table(pos, K)
+    scale_bits = struct.unpack("<I", struct.pack("<f", 1.0 / 16.0))[0]
+    cache.dispatch(0, "kv_rope2", [256, 2 * K, 0, 0, 256, 256, 2, pos * 512], dev(k), dev(tab))
+    cache.dispatch(0, "kv_copy", [512 * K, 0, 0, 0, 0, 0, 0, pos * 512], dev(v))
+    out = torch.empty(K, 16, 256, device="cuda")
+    cache.dispatch(0, "q_dmx", [0, 32, 0, 4, 0, 0, 0, 0])
+    cache.dispatch(0, "attn_dmx2", [pos + 1, 2, scale_bits, K, 0, 0, 2048, 0], dev(q), None, out)
+    cache.dispatch(0, "attn_fd_combine", [pos + 1, 2, scale_bits, K, 0, 0, 2048, 0])
+    ctx.sync()
+    oracle.append(int(fmt), kc, vc, pos, k, v, tab)
+    gk, gv = host_bits(cache, 0)
+    assert np.array_equal(gk, kc) and np.array_equal(gv, vc)
+    want = oracle.attn_ref_f32(int(fmt), kc, vc, 0, pos, q)
+    assert oracle.max_rel(out.cpu().numpy(), want) < TOL[fmt]
+    with pytest.raises(_lib.MkvError) as e:
+        cache.dispatch(0, "rope2", [256, 8, 0, 0, 256, 256, 2, pos * 512], dev(k), dev(tab))  # the f32 cache's writer
+    assert e.value.status == _lib.ERR_INVALID
+    with pytest.raises(_lib.MkvError) as e:
+        cache.dispatch(0, "delta_q", [0] * 8)
+    assert e.value.status == _lib.ERR_UNSUPPORTED
+    cache.close()
+
+
+def test_launch_count_and_profiling(ctx, oracle):
+    cache = kv.KvCache(ctx, kv.KvFormat.F16, 1, 4096)
+    fill_both(oracle, cache, 0, 1000, 130)
+    q = dev(synth.normal(130, synth.S_Q, 0, (4, 16, 256)))
+    out = torch.empty(4, 16, 256, device="cuda")
+    n0 = ctx.launches
+    ctx.prof_enable(True)
+    for _ in range(3):
+        cache.attn_verify(0, 0, 996, q, out)
+    ms, n = ctx.prof_read()
+    ctx.prof_enable(False)
+    assert n == 3 and 0.0 < ms < 100.0
+    assert ctx.launches - n0 == 6  # core + combine per call
+    cache.close()
