@@ -71,7 +71,8 @@ uint64_t mkv_launch_count(const mkv_ctx *ctx);
 /* Kernel timing with CUDA events on the compute stream, off by default. While on, every attention core
  * kernel (verify / prefill) is bracketed by two events; mkv_prof_read blocks on the last one and returns
  * the summed milliseconds and the number of launches since the last read, then clears them. Mirrors the
- * reference's per-dispatch GPU timestamps of "attn.core" (M/engine.rs:1274-1295). */
+ * reference's per-dispatch GPU timestamps of "attn.core" (M/engine.rs:1274-1295). on = 0 switches it off;
+ * on > 0 switches it on and creates that many event pairs ahead of time (more are created as needed). */
 mkv_status mkv_prof_enable(mkv_ctx *ctx, int on);
 mkv_status mkv_prof_read(mkv_ctx *ctx, double *core_ms, uint64_t *core_launches);
 
@@ -79,10 +80,13 @@ mkv_status mkv_prof_read(mkv_ctx *ctx, double *core_ms, uint64_t *core_launches)
  * Replaces the per-layer buffers kc[il], vc[il] (M/engine.rs:493-494,602-603): n_layers x (K, V), each
  * [capacity][2][256] of f16 or f32, zero-filled (wgpu zero-initialises; the tail tile of the attention
  * reads rows past the valid length and masks them, M/dmx.rs:53,60-64).
- * capacity_tokens: rows held here. For an unsharded cache (shard_first = 0) it must satisfy the reference's
- * rule: a multiple of 1024 in [4096, 262144] (M/engine.rs:28-33). A shard may be any multiple of 64. */
-mkv_status mkv_cache_create(mkv_ctx *ctx, mkv_fmt fmt, int n_layers, uint32_t capacity_tokens,
-                            uint32_t shard_first, mkv_cache **out);
+ * context_tokens: the sequence's context, by the reference's rule a multiple of 1024 in [4096, 262144]
+ * (M/engine.rs:28-33). shard_tokens = 0: this cache holds the whole context (shard_first must be 0). Otherwise
+ * it holds the rows [shard_first, shard_first + shard_tokens) only, both multiples of 64 (one shard of a
+ * sequence-sharded context; appends of other rows are skipped, attention goes through the _partial entry).
+ * A ctx destroyed before its caches stays alive until the last of them is destroyed. */
+mkv_status mkv_cache_create(mkv_ctx *ctx, mkv_fmt fmt, int n_layers, uint32_t context_tokens,
+                            uint32_t shard_first, uint32_t shard_tokens, mkv_cache **out);
 void mkv_cache_destroy(mkv_cache *c);
 /* device pointers of a layer's K and V buffers (for tests and for hosts that fill the cache themselves) */
 mkv_status mkv_cache_buffers(mkv_cache *c, int layer, void **k_dev, void **v_dev);

@@ -53,7 +53,7 @@ _SIGS = {
     "mkv_launch_count": (C.c_uint64, [C.c_void_p]),
     "mkv_prof_enable": (C.c_int, [C.c_void_p, C.c_int]),
     "mkv_prof_read": (C.c_int, [C.c_void_p, C.POINTER(C.c_double), C.POINTER(C.c_uint64)]),
-    "mkv_cache_create": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_uint32, C.c_uint32, C.POINTER(C.c_void_p)]),
+    "mkv_cache_create": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(C.c_void_p)]),
     "mkv_cache_destroy": (None, [C.c_void_p]),
     "mkv_cache_buffers": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)]),
     "mkv_cache_len": (C.c_uint32, [C.c_void_p]),

@@ -120,8 +120,8 @@ static mkv_status fill_item(Cache *c, int layer, uint32_t first_pos, uint32_t po
         return MKV_ERR_INVALID;
     }
     const uint64_t end = (uint64_t)pos + ntok;
-    if (end > (uint64_t)MKV_CTX_MAX) {
-        set_error("pos %u + ntok %u exceeds the largest context %d", pos, ntok, MKV_CTX_MAX);
+    if (end > (uint64_t)c->context) {
+        set_error("pos %u + ntok %u exceeds the context %u", pos, ntok, c->context);
         return MKV_ERR_CAPACITY;
     }
     if (first_pos > pos) {
@@ -129,12 +129,10 @@ static mkv_status fill_item(Cache *c, int layer, uint32_t first_pos, uint32_t po
         return MKV_ERR_INVALID;
     }
     const uint32_t shard_end = c->shard_first + c->capacity;
-    if (!partial) {
-        if (c->shard_first != 0 || end > shard_end) {
-            set_error("keys [%u, %u) are not all in this cache [%u, %u): use mkv_attn_verify_partial on shards", first_pos,
-                      (uint32_t)end, c->shard_first, shard_end);
-            return c->shard_first != 0 ? MKV_ERR_INVALID : MKV_ERR_CAPACITY;
-        }
+    if (!partial && !c->whole) {
+        set_error("this cache is the shard [%u, %u) of a context of %u: use mkv_attn_verify_partial", c->shard_first, shard_end,
+                  c->context);
+        return MKV_ERR_INVALID;
     }
     // rows that must be valid: the visible ones held here
     const uint32_t need = (uint32_t)std::min<uint64_t>(end, shard_end);
@@ -271,9 +269,7 @@ mkv_status mkv_ctx_create(int device, void *stream, mkv_ctx **out) {
     return MKV_OK;
 }
 
-void mkv_ctx_destroy(mkv_ctx *h) {
-    Ctx *ctx = reinterpret_cast<Ctx *>(h);
-    if (!ctx) return;
+static void ctx_free(Ctx *ctx) {
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     cudaStreamSynchronize(ctx->copy_stream);
@@ -289,8 +285,17 @@ void mkv_ctx_destroy(mkv_ctx *h) {
     if (ctx->ev_compute) cudaEventDestroy(ctx->ev_compute);
     if (ctx->ev_copy) cudaEventDestroy(ctx->ev_copy);
     if (ctx->copy_stream) cudaStreamDestroy(ctx->copy_stream);
-    if (ctx->own_stream && ctx->stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
+}
+
+void mkv_ctx_destroy(mkv_ctx *h) {
+    Ctx *ctx = reinterpret_cast<Ctx *>(h);
+    if (!ctx || ctx->closing) return;
+    if (ctx->live_caches > 0) { // freed when its last cache goes
+        ctx->closing = true;
+        return;
+    }
+    ctx_free(ctx);
 }
 
 mkv_status mkv_sync(mkv_ctx *h) {
@@ -313,6 +318,16 @@ mkv_status mkv_prof_enable(mkv_ctx *h, int on) {
     if (!ctx) return MKV_ERR_INVALID;
     ctx->prof = on != 0;
     ctx->prof_used = 0;
+    if (on > 0) { // pre-create event pairs so that none is created inside a timed region
+        mkv_status st = use_device(ctx);
+        if (st != MKV_OK) return st;
+        while (ctx->prof_events.size() < (size_t)on) {
+            cudaEvent_t a, b;
+            MKV_CUDA(cudaEventCreate(&a));
+            MKV_CUDA(cudaEventCreate(&b));
+            ctx->prof_events.push_back({a, b});
+        }
+    }
     return MKV_OK;
 }
 
@@ -344,9 +359,10 @@ uint64_t mkv_need_bytes(uint32_t ctx_tokens, mkv_fmt fmt, int n_layers) {
     return kv + partials;
 }
 
-mkv_status mkv_cache_create(mkv_ctx *h, mkv_fmt fmt, int n_layers, uint32_t capacity, uint32_t shard_first, mkv_cache **out) {
+mkv_status mkv_cache_create(mkv_ctx *h, mkv_fmt fmt, int n_layers, uint32_t context, uint32_t shard_first,
+                            uint32_t shard_tokens, mkv_cache **out) {
     Ctx *ctx = reinterpret_cast<Ctx *>(h);
-    if (!ctx || !out) {
+    if (!ctx || !out || ctx->closing) {
         set_error("null argument");
         return MKV_ERR_INVALID;
     }
@@ -359,16 +375,17 @@ mkv_status mkv_cache_create(mkv_ctx *h, mkv_fmt fmt, int n_layers, uint32_t capa
         set_error("n_layers %d outside [1, 256]", n_layers);
         return MKV_ERR_INVALID;
     }
-    if (shard_first == 0) {
-        // M/engine.rs:28-33 check_ctx
-        if (capacity % 1024 != 0 || capacity < MKV_CTX_MIN || capacity > MKV_CTX_MAX) {
-            set_error("context %u: must be a multiple of 1024 between %d and %d", capacity, MKV_CTX_MIN, MKV_CTX_MAX);
-            return MKV_ERR_INVALID;
-        }
-    } else if (capacity == 0 || capacity % 64 != 0 || shard_first % 64 != 0 ||
-               (uint64_t)shard_first + capacity > (uint64_t)MKV_CTX_MAX) {
-        set_error("shard [%u, +%u): first row and size must be multiples of 64 inside [0, %d]", shard_first, capacity,
-                  MKV_CTX_MAX);
+    // M/engine.rs:28-33 check_ctx
+    if (context % 1024 != 0 || context < MKV_CTX_MIN || context > MKV_CTX_MAX) {
+        set_error("context %u: must be a multiple of 1024 between %d and %d", context, MKV_CTX_MIN, MKV_CTX_MAX);
+        return MKV_ERR_INVALID;
+    }
+    const bool whole = shard_tokens == 0;
+    const uint32_t capacity = whole ? context : shard_tokens;
+    if (whole ? shard_first != 0
+              : (capacity % 64 != 0 || shard_first % 64 != 0 || (uint64_t)shard_first + capacity > (uint64_t)context)) {
+        set_error("shard [%u, +%u): first row and size must be multiples of 64 inside the context %u", shard_first,
+                  shard_tokens, context);
         return MKV_ERR_INVALID;
     }
     mkv_status st = use_device(ctx);
@@ -378,8 +395,11 @@ mkv_status mkv_cache_create(mkv_ctx *h, mkv_fmt fmt, int n_layers, uint32_t capa
     c->ctx = ctx;
     c->fmt = fmt;
     c->n_layers = n_layers;
+    c->context = context;
     c->capacity = capacity;
     c->shard_first = shard_first;
+    c->whole = whole;
+    ctx->live_caches++;
     c->elem = fmt == MKV_F16 ? 2 : 4;
     c->buf_bytes = (size_t)capacity * ROW * c->elem;
     c->k.assign(n_layers, nullptr);
@@ -441,7 +461,9 @@ void mkv_cache_destroy(mkv_cache *h) {
     if (c->part_ml) cudaFree(c->part_ml);
     if (c->part_o) cudaFree(c->part_o);
     if (c->ev_snapshot) cudaEventDestroy(c->ev_snapshot);
+    Ctx *ctx = c->ctx;
     delete c;
+    if (--ctx->live_caches == 0 && ctx->closing) ctx_free(ctx);
 }
 
 mkv_status mkv_cache_buffers(mkv_cache *h, int layer, void **k_dev, void **v_dev) {
@@ -505,8 +527,8 @@ static mkv_status append_common(Cache *c, int layer0, int n_layers, uint32_t pos
     }
     const uint64_t end = (uint64_t)pos + ntok;
     const uint32_t shard_end = c->shard_first + c->capacity;
-    if (c->shard_first == 0 ? end > shard_end : end > (uint64_t)MKV_CTX_MAX) {
-        set_error("rows [%u, %u) do not fit the cache of %u rows", pos, (uint32_t)end, c->capacity);
+    if (end > (uint64_t)c->context) {
+        set_error("rows [%u, %u) do not fit the context of %u rows", pos, (uint32_t)end, c->context);
         return MKV_ERR_CAPACITY;
     }
     mkv_status st = use_device(c->ctx);
@@ -629,7 +651,7 @@ mkv_status mkv_attn_prefill(mkv_cache *h, int layer, uint32_t first_pos, uint32_
         set_error("q and out must be 16-byte aligned");
         return MKV_ERR_INVALID;
     }
-    if (c->shard_first != 0) {
+    if (!c->whole) {
         set_error("prefill attention runs on unsharded caches");
         return MKV_ERR_UNSUPPORTED;
     }
@@ -695,9 +717,12 @@ mkv_status mkv_snapshot(mkv_cache *h, uint32_t p, void *dst, size_t cap, size_t 
         set_error("null argument");
         return MKV_ERR_INVALID;
     }
-    if (p > c->len) {
-        set_error("snapshot of %u rows but only %u are valid", p, c->len);
-        return MKV_ERR_STATE;
+    {
+        const uint32_t upto = std::min(p, c->shard_first + c->capacity); // the rows of [0, p) held here
+        if (upto > c->shard_first && upto > c->len) {
+            set_error("snapshot of %u rows but only %u are valid", p, c->len);
+            return MKV_ERR_STATE;
+        }
     }
     const size_t need = mkv_snapshot_bytes(h, p);
     if (cap < need) {
@@ -750,10 +775,11 @@ mkv_status mkv_restore(mkv_cache *h, uint32_t p, const void *src, size_t bytes) 
         return MKV_ERR_INVALID;
     }
     const uint32_t end = c->shard_first + c->capacity;
-    if (c->shard_first == 0 && p > end) {
-        set_error("restore of %u rows into a cache of %u", p, c->capacity);
+    if (p > c->context) {
+        set_error("restore of %u rows into a context of %u", p, c->context);
         return MKV_ERR_CAPACITY;
     }
+    (void)end;
     const size_t need = mkv_snapshot_bytes(h, p);
     if (bytes != need) {
         set_error("restore payload is %zu bytes, %u rows of this cache are %zu", bytes, p, need);

@@ -63,7 +63,6 @@ struct Ctx {
     int device = 0;
     int sm_count = 148;
     cudaStream_t stream = nullptr;
-    bool own_stream = false;
     cudaStream_t copy_stream = nullptr;
     cudaEvent_t ev_compute = nullptr; // compute -> copy ordering
     cudaEvent_t ev_copy = nullptr;    // copy -> compute ordering
@@ -81,14 +80,19 @@ struct Ctx {
     cudaEvent_t slot_done[SLOTS] = {};
     bool slot_used[SLOTS] = {};
     int slot_next = 0;
+    // lifetime: caches hold a reference; a ctx destroyed while caches live is freed with the last of them
+    int live_caches = 0;
+    bool closing = false;
 };
 
 struct Cache {
     Ctx *ctx = nullptr;
     mkv_fmt fmt = MKV_F16;
     int n_layers = 0;
-    uint32_t capacity = 0;
+    uint32_t context = 0;  // tokens of the whole sequence's context
+    uint32_t capacity = 0; // rows held here
     uint32_t shard_first = 0;
+    bool whole = true;     // holds the whole context (not a sequence shard)
     uint32_t len = 0; // global position after the last valid row
     size_t elem = 2;
     size_t buf_bytes = 0;

@@ -100,7 +100,8 @@ class KvContext:
     def launches(self) -> int:
         return int(_lib.lib().mkv_launch_count(self._h))
 
-    def prof_enable(self, on: bool) -> None:
+    def prof_enable(self, on: int) -> None:
+        """0 = off; n > 0 = on, with n event pairs created ahead of time."""
         check(_lib.lib().mkv_prof_enable(self._h, int(on)))
 
     def prof_read(self) -> tuple[float, int]:
@@ -135,11 +136,16 @@ class KvContext:
 class KvCache:
     """The per-layer K and V buffers of the attention layers and the operators that touch them (mkv_cache)."""
 
-    def __init__(self, ctx: KvContext, fmt: KvFormat, n_layers: int, capacity: int, shard_first: int = 0):
+    def __init__(self, ctx: KvContext, fmt: KvFormat, n_layers: int, context: int, shard_first: int = 0,
+                 shard_tokens: int = 0):
+        """context: the sequence's context (check_ctx rule). shard_tokens = 0: the whole context lives here;
+        otherwise only rows [shard_first, shard_first + shard_tokens)."""
         self.ctx, self.fmt, self.n_layers = ctx, KvFormat(fmt), n_layers
-        self.capacity, self.shard_first = capacity, shard_first
+        self.context = context
+        self.capacity, self.shard_first = (shard_tokens or context), shard_first
         self._h = C.c_void_p()
-        check(_lib.lib().mkv_cache_create(ctx._h, int(fmt), n_layers, capacity, shard_first, C.byref(self._h)))
+        check(_lib.lib().mkv_cache_create(ctx._h, int(fmt), n_layers, context, shard_first, shard_tokens,
+                                          C.byref(self._h)))
 
     # -- bookkeeping
     def __len__(self) -> int:

@@ -294,7 +294,7 @@ def test_sequence_shards_on_one_gpu(ctx, oracle, fmt, n_shards):
     per = total // n_shards
     whole = kv.KvCache(ctx, fmt, 1, total)
     kc, vc = fill_both(oracle, whole, 0, total, 71)
-    shards = [kv.KvCache(ctx, fmt, 1, per, shard_first=g * per) for g in range(n_shards)]
+    shards = [kv.KvCache(ctx, fmt, 1, total, shard_first=g * per, shard_tokens=per) for g in range(n_shards)]
     for p in range(0, total, 2048):  # every shard sees every append and keeps its own rows
         k = dev(synth.normal(71, synth.S_K, p, (2048, 2, 256)))
         v = dev(synth.normal(71, synth.S_V, p, (2048, 2, 256)))
@@ -434,7 +434,7 @@ def test_snapshot_of_shards_concatenates_to_the_whole(ctx, oracle):
     fmt, total, per = kv.KvFormat.F16, 4096, 1024
     whole = kv.KvCache(ctx, fmt, 1, total)
     fill_both(oracle, whole, 0, 3000, 110)
-    shards = [kv.KvCache(ctx, fmt, 1, per, shard_first=g * per) for g in range(4)]
+    shards = [kv.KvCache(ctx, fmt, 1, total, shard_first=g * per, shard_tokens=per) for g in range(4)]
     p = 2500
     hk, hv = host_bits(whole, 0)
     for g, s in enumerate(shards):
