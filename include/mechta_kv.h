@@ -106,7 +106,7 @@ uint64_t mkv_cache_device_bytes(const mkv_cache *c);
  * already rotated. Token t goes to global position pos + t; rows outside this cache's shard are skipped.
  * Afterwards the valid length is pos + ntok (rows beyond it, e.g. refused drafts, are forgotten).
  * Products and the sum/difference of the rotation are rounded separately (no FMA); f16 stores round to
- * nearest even. 1 <= ntok <= 4096. */
+ * nearest even. 1 <= ntok, pos + ntok <= context. */
 mkv_status mkv_append(mkv_cache *c, int layer, uint32_t pos, uint32_t ntok, const float *k_dev,
                       const float *v_dev, const float *rope_tab_dev);
 /* the same for every layer in one launch: k_dev/v_dev/rope as above with a leading [n_layers] axis on

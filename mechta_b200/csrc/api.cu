@@ -3,6 +3,7 @@
 #include <math.h>
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <algorithm>
@@ -22,6 +23,7 @@ void set_error(const char *fmt, ...) {
 }
 
 mkv_status prefill_setup_device();
+mkv_status append_setup_device();
 mkv_status launch_prefill_f16_mma(Ctx *ctx, Cache *c, int layer, uint32_t first_pos, uint32_t pos0, uint32_t ntok,
                                   const float *q, float *out);
 
@@ -62,6 +64,16 @@ static mkv_status make_tensor_map(CUtensorMap *out, mkv_fmt fmt, void *base, uin
         return MKV_ERR_CUDA;
     }
     return MKV_OK;
+}
+
+// MKV_PHASE=1 in the environment: kernels only stream their tiles (to time the loads alone; results are wrong)
+static uint32_t measure_phase() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("MKV_PHASE");
+        v = e ? atoi(e) : 0;
+    }
+    return (uint32_t)v;
 }
 
 static mkv_status use_device(Ctx *ctx) {
@@ -157,6 +169,7 @@ static mkv_status fill_item(Cache *c, int layer, uint32_t first_pos, uint32_t po
     it->key_lo = c->shard_first;
     it->key_hi = shard_end;
     it->partial = partial ? 1u : 0u;
+    it->phase = measure_phase();
     if (hi > lo) {
         it->tile_begin = lo / T;
         it->tile_end = (hi + T - 1) / T;
@@ -198,7 +211,7 @@ static mkv_status verify_common(Cache *c, int layer, uint32_t first_pos, uint32_
     plan_items(c->ctx, &it, 1);
     Cache *cc[1] = {c};
     if ((st = place_scratch(cc, &it, 1)) != MKV_OK) return st;
-    return launch_verify(c->ctx, c->fmt, &it, 1, false);
+    return launch_verify(c->ctx, c->fmt, &it, 1, false, &c->maps_host[2 * layer], &c->maps_host[2 * layer + 1]);
 }
 
 } // namespace mkv
@@ -262,8 +275,12 @@ mkv_status mkv_ctx_create(int device, void *stream, mkv_ctx **out) {
     MKV_CUDA(cudaMalloc(&ctx->items_dev, ring));
     MKV_CUDA(cudaHostAlloc(&ctx->items_host, ring, cudaHostAllocDefault));
     for (int i = 0; i < Ctx::SLOTS; i++) MKV_CUDA(cudaEventCreateWithFlags(&ctx->slot_done[i], cudaEventDisableTiming));
+    MKV_CUDA(cudaMalloc(&ctx->counters_dev, sizeof(uint32_t) * Ctx::SLOT_ITEMS));
+    MKV_CUDA(cudaMemset(ctx->counters_dev, 0, sizeof(uint32_t) * Ctx::SLOT_ITEMS));
+    ctx->counter_base.assign(Ctx::SLOT_ITEMS, 0u);
     mkv_status st = verify_setup_device();
     if (st == MKV_OK) st = prefill_setup_device();
+    if (st == MKV_OK) st = append_setup_device();
     if (st != MKV_OK) return st;
     *out = reinterpret_cast<mkv_ctx *>(ctx);
     return MKV_OK;
@@ -280,6 +297,7 @@ static void ctx_free(Ctx *ctx) {
     for (int i = 0; i < Ctx::SLOTS; i++)
         if (ctx->slot_done[i]) cudaEventDestroy(ctx->slot_done[i]);
     if (ctx->items_dev) cudaFree(ctx->items_dev);
+    if (ctx->counters_dev) cudaFree(ctx->counters_dev);
     if (ctx->items_host) cudaFreeHost(ctx->items_host);
     if (ctx->dev_status) cudaFree(ctx->dev_status);
     if (ctx->ev_compute) cudaEventDestroy(ctx->ev_compute);
@@ -420,11 +438,16 @@ mkv_status mkv_cache_create(mkv_ctx *h, mkv_fmt fmt, int n_layers, uint32_t cont
             return fail(MKV_ERR_CUDA);
         }
     }
-    std::vector<CUtensorMap> maps(2 * (size_t)n_layers);
+    // two sets of tensor maps per layer: boxes of the verify tile, then boxes of the prefill tile
+    std::vector<CUtensorMap> &maps = c->maps_host;
+    maps.resize(4 * (size_t)n_layers);
     const uint32_t box_rows = fmt == MKV_F16 ? TILE : TILE32;
+    const uint32_t pf_rows = fmt == MKV_F16 ? PF_TILE : TILE32;
     for (int l = 0; l < n_layers; l++) {
         if ((st = make_tensor_map(&maps[2 * l], fmt, c->k[l], capacity, box_rows)) != MKV_OK) return fail(st);
         if ((st = make_tensor_map(&maps[2 * l + 1], fmt, c->v[l], capacity, box_rows)) != MKV_OK) return fail(st);
+        if ((st = make_tensor_map(&maps[2 * (n_layers + l)], fmt, c->k[l], capacity, pf_rows)) != MKV_OK) return fail(st);
+        if ((st = make_tensor_map(&maps[2 * (n_layers + l) + 1], fmt, c->v[l], capacity, pf_rows)) != MKV_OK) return fail(st);
     }
     if (cudaMalloc(&c->maps_dev, maps.size() * sizeof(CUtensorMap)) != cudaSuccess ||
         cudaMalloc(&c->kptrs_dev, n_layers * sizeof(void *)) != cudaSuccess ||
@@ -517,8 +540,8 @@ static mkv_status append_common(Cache *c, int layer0, int n_layers, uint32_t pos
         set_error("null argument");
         return MKV_ERR_INVALID;
     }
-    if (ntok < 1 || ntok > 4096) {
-        set_error("ntok %u outside [1, 4096]", ntok);
+    if (ntok < 1 || ntok > (uint32_t)MKV_CTX_MAX) {
+        set_error("ntok %u outside [1, %d]", ntok, MKV_CTX_MAX);
         return MKV_ERR_INVALID;
     }
     if (((uintptr_t)k & 15u) || ((uintptr_t)v & 15u) || ((uintptr_t)tab & 15u)) {
@@ -633,7 +656,7 @@ mkv_status mkv_attn_verify_batch(mkv_ctx *h, const mkv_verify_item *items, int n
     if (st != MKV_OK) return st;
     plan_items(ctx, its.data(), n);
     if ((st = place_scratch(caches.data(), its.data(), n)) != MKV_OK) return st;
-    return launch_verify(ctx, fmt, its.data(), n, true);
+    return launch_verify(ctx, fmt, its.data(), n, true, nullptr, nullptr);
 }
 
 mkv_status mkv_attn_prefill(mkv_cache *h, int layer, uint32_t first_pos, uint32_t pos0, uint32_t ntok, const float *q,
@@ -687,7 +710,7 @@ mkv_status mkv_attn_prefill(mkv_cache *h, int layer, uint32_t first_pos, uint32_
         }
         plan_items(c->ctx, its.data(), groups);
         if ((st = place_scratch(caches.data(), its.data(), groups)) != MKV_OK) return st;
-        if ((st = launch_verify(c->ctx, c->fmt, its.data(), groups, true)) != MKV_OK) return st;
+        if ((st = launch_verify(c->ctx, c->fmt, its.data(), groups, true, nullptr, nullptr)) != MKV_OK) return st;
         done += 4u * groups;
     }
     return MKV_OK;
@@ -713,7 +736,7 @@ size_t mkv_snapshot_bytes(const mkv_cache *h, uint32_t p) {
 
 mkv_status mkv_snapshot(mkv_cache *h, uint32_t p, void *dst, size_t cap, size_t *written) {
     Cache *c = reinterpret_cast<Cache *>(h);
-    if (!c || !dst) {
+    if (!c || (!dst && mkv_snapshot_bytes(h, p) != 0)) {
         set_error("null argument");
         return MKV_ERR_INVALID;
     }
@@ -770,7 +793,7 @@ mkv_status mkv_snapshot_wait(mkv_cache *h) {
 
 mkv_status mkv_restore(mkv_cache *h, uint32_t p, const void *src, size_t bytes) {
     Cache *c = reinterpret_cast<Cache *>(h);
-    if (!c || !src) {
+    if (!c || (!src && bytes != 0)) {
         set_error("null argument");
         return MKV_ERR_INVALID;
     }

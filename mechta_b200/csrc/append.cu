@@ -84,6 +84,12 @@ append_kernel(void *const *__restrict__ kbufs, void *const *__restrict__ vbufs, 
     }
 }
 
+mkv_status append_setup_device() {
+    MKV_CUDA(cudaFuncSetAttribute(append_kernel<true>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
+    MKV_CUDA(cudaFuncSetAttribute(append_kernel<false>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
+    return MKV_OK;
+}
+
 mkv_status launch_append(Ctx *ctx, mkv_fmt fmt, void *const *kbufs, void *const *vbufs, int n_layers,
                          size_t layer_stride_in, uint32_t row_first, uint32_t capacity, uint32_t pos, uint32_t ntok,
                          const float *k, const float *v, const float *tab, uint32_t which) {

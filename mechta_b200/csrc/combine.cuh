@@ -1,0 +1,147 @@
+// Log-sum-exp merge of split-K pieces, done inside the attention kernels by the CTAs that finish last.
+//
+// Arithmetic: attn_fd_combine of the reference (W/ops.wgsl:529-537) over this library's pieces:
+//   M = max_s m_s;  tot = sum_s e^(m_s - M) l_s;  acc[d] = sum_s e^(m_s - M) O_s[d];  out = acc / tot.
+// Scheduling: every CTA publishes its piece, then takes a ticket from a counter in global memory. The last
+// R = min(CTAs of the item, 64) arrivals wait (bounded) until the counter shows that all pieces are there and
+// each merges a share of the item's 64 rows. Only CTAs that have already finished their own work ever wait,
+// and fewer of them than there are SMs, so the others always make progress.
+#pragma once
+#include "internal.cuh"
+
+namespace mkv {
+
+constexpr int FIN_MAX_THREADS = 512;
+
+struct FinishSmem {
+    float e_s[MAX_SPLITS];
+    float red[FIN_MAX_THREADS / 32];
+    float tot, M;
+    uint32_t ticket, ok;
+    float4 part[FIN_MAX_THREADS / 64][64];
+};
+
+// One row (kvh * 32 + row) of one item, by all NT threads of the CTA.
+template <int NT>
+__device__ __forceinline__ void merge_row(const VerifyItem &it, uint32_t r, FinishSmem &sm) {
+    constexpr int GROUPS = NT / 64;
+    constexpr int NW = NT / 32;
+    const uint32_t kvh = r >> 5, row = r & 31u, tok = row >> 3, head = 8u * kvh + (row & 7u);
+    const uint32_t tid = threadIdx.x;
+    if (tok >= it.ntok) {
+        if (it.partial && tid < 258u) // rows of tokens beyond the step: the empty record
+            it.out[(size_t)(tok * 16u + head) * REC + tid] = tid == 0 ? NEG_BIG : 0.0f;
+        return;
+    }
+    const uint32_t ns = it.nsplit;
+    const float2 *ml = reinterpret_cast<const float2 *>(it.part_ml) + (size_t)kvh * ns * 32u + row;
+    float m = NEG_BIG, l = 0.0f;
+    if (tid < ns) {
+        const float2 x = __ldcg(ml + (size_t)tid * 32u);
+        m = x.x;
+        l = x.y;
+    }
+    float M = m;
+#pragma unroll
+    for (int sh = 16; sh > 0; sh >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, sh));
+    __syncthreads(); // the previous row's reads of the shared scratch are over
+    if ((tid & 31u) == 0) sm.red[tid >> 5] = M;
+    __syncthreads();
+    if (tid < 32) {
+        float x = tid < NW ? sm.red[tid] : NEG_BIG;
+#pragma unroll
+        for (int sh = 16; sh > 0; sh >>= 1) x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, sh));
+        if (tid == 0) sm.M = x;
+    }
+    __syncthreads();
+    M = sm.M;
+    const float e = tid < ns ? expf(m - M) : 0.0f;
+    if (tid < ns) sm.e_s[tid] = e;
+    float t = e * l;
+#pragma unroll
+    for (int sh = 16; sh > 0; sh >>= 1) t += __shfl_xor_sync(0xffffffffu, t, sh);
+    if ((tid & 31u) == 0) sm.red[tid >> 5] = t; // the maxima were all read before the barrier above
+    __syncthreads();
+    if (tid < 32) {
+        float x = tid < NW ? sm.red[tid] : 0.0f;
+#pragma unroll
+        for (int sh = 16; sh > 0; sh >>= 1) x += __shfl_xor_sync(0xffffffffu, x, sh);
+        if (tid == 0) sm.tot = x;
+    }
+    const uint32_t grp = tid >> 6, d4 = tid & 63u;
+    const float4 *po = reinterpret_cast<const float4 *>(it.part_o + ((size_t)kvh * ns * 32u + row) * 256u) + d4;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    // rounds of five pieces per group: the five loads of a round are issued before any is used
+    for (uint32_t s0 = grp; s0 < ns; s0 += GROUPS * 5u) {
+        float4 x[5];
+#pragma unroll
+        for (int i = 0; i < 5; i++) {
+            const uint32_t s = s0 + GROUPS * i;
+            x[i] = s < ns ? __ldcg(po + (size_t)s * 2048u) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int i = 0; i < 5; i++) {
+            const uint32_t s = s0 + GROUPS * i;
+            const float w = s < ns ? sm.e_s[s] : 0.0f;
+            acc.x += w * x[i].x;
+            acc.y += w * x[i].y;
+            acc.z += w * x[i].z;
+            acc.w += w * x[i].w;
+        }
+    }
+    sm.part[grp][d4] = acc;
+    __syncthreads();
+    if (tid < 64) {
+        float4 a = sm.part[0][tid];
+#pragma unroll
+        for (int g = 1; g < GROUPS; g++) {
+            const float4 b = sm.part[g][tid];
+            a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+        }
+        const float tot = sm.tot;
+        if (it.partial) {
+            float *rec = it.out + (size_t)(tok * 16u + head) * REC; // records are 8-byte aligned only
+            *reinterpret_cast<float2 *>(rec + 2 + 4 * tid) = make_float2(a.x, a.y);
+            *reinterpret_cast<float2 *>(rec + 4 + 4 * tid) = make_float2(a.z, a.w);
+            if (tid == 0) *reinterpret_cast<float2 *>(rec) = make_float2(M, tot);
+        } else {
+            const float inv = 1.0f / tot;
+            *reinterpret_cast<float4 *>(it.out + (size_t)tok * 4096u + (size_t)head * 256u + 4 * tid) =
+                make_float4(a.x * inv, a.y * inv, a.z * inv, a.w * inv);
+        }
+    }
+}
+
+// Called by every thread of every CTA of an item after the CTA's piece has been written to global memory.
+// `sm` must not alias anything still in use. Returns after this CTA's share of the merge (possibly none).
+template <int NT>
+__device__ __forceinline__ void finish_item(const VerifyItem &it, FinishSmem &sm, uint32_t *status) {
+    const uint32_t total = 2u * it.nsplit;
+    __threadfence(); // this thread's part of the piece is visible device-wide before the ticket is taken
+    __syncthreads();
+    if (threadIdx.x == 0) sm.ticket = atomicAdd(it.counter, 1u) - it.ticket_base;
+    __syncthreads();
+    const uint32_t ticket = sm.ticket;
+    const uint32_t R = total < 64u ? total : 64u;
+    if (ticket < total - R) return; // not among the last R: nothing to merge
+    if (threadIdx.x == 0) {
+        // wait until every CTA of the item has published; bounded, in case a CTA never arrives
+        const long long t0 = clock64();
+        bool ok = true;
+        while (*reinterpret_cast<volatile uint32_t *>(it.counter) - it.ticket_base < total) {
+            __nanosleep(64);
+            if (clock64() - t0 > 4000000000ll) {
+                ok = false;
+                break;
+            }
+        }
+        if (!ok) atomicOr(status, DEV_ERR_WAIT_TIMEOUT);
+        sm.ok = ok ? 1u : 0u;
+    }
+    __syncthreads();
+    if (!sm.ok) return;
+    __threadfence();
+    for (uint32_t r = ticket - (total - R); r < 64u; r += R) merge_row<NT>(it, r, sm);
+}
+
+} // namespace mkv

@@ -13,7 +13,8 @@
 namespace mkv {
 
 constexpr int HQ = 16, HKV = 2, D = 256, GROUP = 8, ROW = 512, REC = 258;
-constexpr int TILE = 64;            // keys per attention tile, f16 cache (as the reference, M/dmx.rs:53)
+constexpr int TILE = 32;            // keys per verify tile, f16 cache
+constexpr int PF_TILE = 64;         // keys per prefill tile (as the reference, W/fa_mx.wgsl:27)
 constexpr int TILE32 = 32;          // keys per tile, f32 cache
 constexpr float NEG_BIG = -3.0e38f; // mask value of the reference (W/ops.wgsl:339)
 constexpr float NEG_TEST = -1.0e38f;
@@ -54,6 +55,17 @@ struct VerifyItem {
     uint32_t tiles_per_split;
     uint32_t cta_begin; // first CTA of this item in the flattened grid (2 * nsplit CTAs per item)
     uint32_t partial;   // 1: write the un-normalised record instead of the final output
+    uint32_t *counter;  // arrival counter of this item's CTAs (global memory), never reset
+    uint32_t ticket_base; // value of the counter before this launch
+    uint32_t phase;     // measurement only, as the reference's p.f1 phases: 0 = everything, 1 = tile loads only
+};
+
+// What a single (non-batched) launch carries in the kernel's parameter space: the item and its two tensor
+// maps, so that the TMA unit does not have to fetch the maps from global memory first.
+struct VerifyLaunch {
+    VerifyItem item;
+    alignas(64) CUtensorMap kmap;
+    alignas(64) CUtensorMap vmap;
 };
 
 struct Ctx;
@@ -80,6 +92,8 @@ struct Ctx {
     cudaEvent_t slot_done[SLOTS] = {};
     bool slot_used[SLOTS] = {};
     int slot_next = 0;
+    uint32_t *counters_dev = nullptr;          // [SLOT_ITEMS] arrival counters, zeroed once
+    std::vector<uint32_t> counter_base;        // host shadow: value of each counter after the launches so far
     // lifetime: caches hold a reference; a ctx destroyed while caches live is freed with the last of them
     int live_caches = 0;
     bool closing = false;
@@ -99,7 +113,8 @@ struct Cache {
     std::vector<void *> k, v;
     void **kptrs_dev = nullptr;      // [n_layers] device copies of k / v
     void **vptrs_dev = nullptr;
-    CUtensorMap *maps_dev = nullptr; // [n_layers][2]: verify tiles; [n_layers][2] more: none yet
+    std::vector<CUtensorMap> maps_host;
+    CUtensorMap *maps_dev = nullptr; // [n_layers][2] with the verify tile's box, then [n_layers][2] with the prefill tile's
     float *part_ml = nullptr;        // split-K scratch, shared by the layers (stream-ordered), grow-only
     float *part_o = nullptr;
     size_t scratch_pieces = 0;       // pieces (KV head x split) the scratch holds
@@ -112,7 +127,8 @@ mkv_status launch_append(Ctx *ctx, mkv_fmt fmt, void *const *kbufs, void *const 
                          size_t layer_stride_in, uint32_t row_first, uint32_t capacity, uint32_t pos, uint32_t ntok,
                          const float *k, const float *v, const float *tab, uint32_t which /*1 = K, 2 = V, 3 = both*/);
 // items_host[0..n) are planned; batch = false: n == 1 and the item travels in the kernel's parameter space
-mkv_status launch_verify(Ctx *ctx, mkv_fmt fmt, const VerifyItem *items_host, int n, bool batch);
+mkv_status launch_verify(Ctx *ctx, mkv_fmt fmt, VerifyItem *items_host, int n, bool batch, const CUtensorMap *kmap_host,
+                         const CUtensorMap *vmap_host);
 mkv_status verify_setup_device();
 mkv_status launch_combine_shards(Ctx *ctx, const float *recs, int n_shards, uint32_t ntok, float *out);
 mkv_status launch_prefill(Ctx *ctx, Cache *c, int layer, uint32_t first_pos, uint32_t pos0, uint32_t ntok,

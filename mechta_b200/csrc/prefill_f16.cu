@@ -36,7 +36,7 @@ prefill_f16_mma_kernel(const CUtensorMap *__restrict__ kmap, const CUtensorMap *
     const uint32_t tok0 = grp * 16u;
     const uint32_t last_tok = min(tok0 + 15u, ntok - 1u);
     const uint32_t lim = pos0 + 1u + last_tok; // keys seen by the group: [first_pos, lim)
-    const uint32_t t0 = first_pos / TILE, t1 = (lim + TILE - 1u) / TILE;
+    const uint32_t t0 = first_pos / PF_TILE, t1 = (lim + PF_TILE - 1u) / PF_TILE;
     const uint32_t nt = t1 - t0;
     const uint32_t bar0 = smem_base + PF_OFF_BAR;
 
@@ -49,7 +49,7 @@ prefill_f16_mma_kernel(const CUtensorMap *__restrict__ kmap, const CUtensorMap *
     auto issue = [&](uint32_t j) {
         const uint32_t s = j % PF_NST, bar = bar0 + 8u * s;
         const uint32_t dst = smem_base + s * PF_STAGE;
-        const int y = (int)((t0 + j) * TILE - row0);
+        const int y = (int)((t0 + j) * PF_TILE - row0);
         const int x = (int)(kvh * 256u);
         mbar_expect_tx(bar, PF_STAGE);
 #pragma unroll
@@ -108,7 +108,7 @@ prefill_f16_mma_kernel(const CUtensorMap *__restrict__ kmap, const CUtensorMap *
             atomicOr(status, DEV_ERR_WAIT_TIMEOUT);
         }
         const uint32_t Kb = smem_base + s * PF_STAGE, Vb = Kb + 4 * PF_SUB;
-        const uint32_t key_base = (t0 + j) * TILE;
+        const uint32_t key_base = (t0 + j) * PF_TILE;
 
         // ---- S (16 x 64) = Q K^T ----
         float sc[8][4];
@@ -137,7 +137,7 @@ prefill_f16_mma_kernel(const CUtensorMap *__restrict__ kmap, const CUtensorMap *
         }
 
         // ---- scale, mask, online softmax in registers ----
-        const bool need_mask = key_base + TILE > full_below || key_base < first_pos;
+        const bool need_mask = key_base + PF_TILE > full_below || key_base < first_pos;
         float mx[2] = {NEG_BIG, NEG_BIG};
 #pragma unroll
         for (int n = 0; n < 8; n++)
@@ -221,13 +221,14 @@ prefill_f16_mma_kernel(const CUtensorMap *__restrict__ kmap, const CUtensorMap *
 
 mkv_status prefill_setup_device() {
     MKV_CUDA(cudaFuncSetAttribute(prefill_f16_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM));
+    MKV_CUDA(cudaFuncSetAttribute(prefill_f16_mma_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
     return MKV_OK;
 }
 
 mkv_status launch_prefill_f16_mma(Ctx *ctx, Cache *c, int layer, uint32_t first_pos, uint32_t pos0, uint32_t ntok,
                                   const float *q, float *out) {
     const dim3 grid((ntok + 15u) / 16u, 2);
-    prefill_f16_mma_kernel<<<grid, 256, PF_SMEM, ctx->stream>>>(c->maps_dev + 2 * layer, c->maps_dev + 2 * layer + 1, q, out,
+    prefill_f16_mma_kernel<<<grid, 256, PF_SMEM, ctx->stream>>>(c->maps_dev + 2 * (c->n_layers + layer), c->maps_dev + 2 * (c->n_layers + layer) + 1, q, out,
                                                                 first_pos, pos0, ntok, c->shard_first, ctx->dev_status);
     ctx->launches++;
     MKV_CUDA(cudaGetLastError());

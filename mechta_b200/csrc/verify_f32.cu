@@ -9,6 +9,7 @@
 //  - scores: thread = (key, group of 4 rows); the K row chunk is one 16-byte shared load, Q chunks are
 //    broadcast loads, 16 FMA per 5 loads;
 //  - P V: thread = (4 dims, group of 8 rows); one 16-byte V load and two broadcast P loads per 32 FMA.
+#include "combine.cuh"
 #include "internal.cuh"
 #include "ptx.cuh"
 
@@ -27,13 +28,13 @@ constexpr uint32_t V32_SMEM = V32_OFF_BAR + V32_NST * 8 + 1024;
 constexpr long long WAIT_LIMIT32 = 4000000000ll;
 
 __global__ void __launch_bounds__(256, 1)
-verify_f32_kernel(const VerifyItem *__restrict__ items, int n_items, const __grid_constant__ VerifyItem single,
+verify_f32_kernel(const VerifyItem *__restrict__ items, int n_items, const __grid_constant__ VerifyLaunch single,
                   uint32_t *__restrict__ status) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *smem = smem_raw + (smem_base - smem_u32(smem_raw));
 
-    const VerifyItem *itp = &single;
+    const VerifyItem *itp = &single.item;
     if (items != nullptr) {
         int lo = 0;
         for (int i = 1; i < n_items; i++)
@@ -48,7 +49,7 @@ verify_f32_kernel(const VerifyItem *__restrict__ items, int n_items, const __gri
     const uint32_t t0 = it.tile_begin + split * it.tiles_per_split;
     const uint32_t t1 = min(t0 + it.tiles_per_split, it.tile_end);
     const uint32_t nt = t1 - t0;
-    const CUtensorMap *kmap = it.kmap, *vmap = it.vmap;
+    const CUtensorMap *kmap = items ? it.kmap : &single.kmap, *vmap = items ? it.vmap : &single.vmap;
     const uint32_t bar0 = smem_base + V32_OFF_BAR;
     const uint32_t nrow = 8u * it.ntok;
 
@@ -203,14 +204,17 @@ verify_f32_kernel(const VerifyItem *__restrict__ items, int n_items, const __gri
             *reinterpret_cast<float4 *>(po + (size_t)(8u * rq + r) * 256u + 4u * dg) =
                 make_float4(acc[r][0], acc[r][1], acc[r][2], acc[r][3]);
     }
+    // the CTAs that finish last merge the pieces (scratch in the ring, which is drained by now)
+    finish_item<256>(it, *reinterpret_cast<FinishSmem *>(smem), status);
 }
 
 mkv_status verify_f32_setup_device() {
     MKV_CUDA(cudaFuncSetAttribute(verify_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)V32_SMEM));
+    MKV_CUDA(cudaFuncSetAttribute(verify_f32_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
     return MKV_OK;
 }
 
-mkv_status launch_verify_f32(Ctx *ctx, const VerifyItem *items_dev, int n, const VerifyItem &single, uint32_t total_ctas) {
+mkv_status launch_verify_f32(Ctx *ctx, const VerifyItem *items_dev, int n, const VerifyLaunch &single, uint32_t total_ctas) {
     verify_f32_kernel<<<total_ctas, 256, V32_SMEM, ctx->stream>>>(items_dev, n, single, ctx->dev_status);
     ctx->launches++;
     MKV_CUDA(cudaGetLastError());
