@@ -344,20 +344,28 @@ def run_decode(args, workload):
         launches = ctx.launches - n0
         clocks = clk.summary()
 
-        # ---- the same steps once more with a pair of CUDA events around every attention kernel: the
-        # dominant kernel's own duration for the roofline (the events cost time, so this pass is not `value`)
+        # ---- the same steps once more with one pair of CUDA events per step around its 10 attention launches
+        # (nothing else runs between them): the dominant kernel's average launch duration for the roofline.
+        # A pair per launch would add its own few microseconds to every short kernel.
         prof_steps = min(steps, 200)
         cache.truncate(min(pos_timed, len(cache)))
         pos = pos_timed
-        ctx.prof_enable(N_LAYERS * prof_steps + 8)
-        ctx.prof_read()
+        pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(prof_steps)]
         core_bytes = 0
-        for s in range(warmup, warmup + prof_steps):
+        for i, s in enumerate(range(warmup, warmup + prof_steps)):
             lo, hi = cache.shard_first, cache.shard_first + cache.capacity
             core_bytes += N_LAYERS * max(0, min(pos + 4, hi) - lo) * per_pos
-            pos = one_step(s, pos)
-        core_ms, core_n = ctx.prof_read()
-        ctx.prof_enable(0)
+            r = s % inp.ring
+            cache.append_layers(pos, inp.k[r], inp.v[r], inp.tab_at(pos))
+            pairs[i][0].record(stream)
+            for l in range(N_LAYERS):
+                attn(l, pos, inp.q[r, l], out[l])
+            pairs[i][1].record(stream)
+            pos = pos + 1 + int(accepts[s])
+            cache.truncate(min(pos, len(cache)))
+        torch.cuda.synchronize()
+        core_ms = sum(a.elapsed_time(b) for a, b in pairs)
+        core_n = N_LAYERS * prof_steps
 
         # ---- end to end through the public API from pinned host buffers
         e2e_steps = min(steps, 200)

@@ -170,6 +170,7 @@ static mkv_status fill_item(Cache *c, int layer, uint32_t first_pos, uint32_t po
     it->key_hi = shard_end;
     it->partial = partial ? 1u : 0u;
     it->phase = measure_phase();
+    it->safe_below = std::min(pos, c->last_write_pos);
     if (hi > lo) {
         it->tile_begin = lo / T;
         it->tile_end = (hi + T - 1) / T;
@@ -265,6 +266,10 @@ mkv_status mkv_ctx_create(int device, void *stream, mkv_ctx **out) {
     if (!ctx) return MKV_ERR_NOMEM;
     ctx->device = device;
     ctx->sm_count = prop.multiProcessorCount;
+    {
+        const char *e = getenv("MKV_PDL");
+        ctx->pdl = !(e && e[0] == '0');
+    }
     ctx->stream = (cudaStream_t)stream; // NULL = the legacy default stream
     MKV_CUDA(cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking));
     MKV_CUDA(cudaEventCreateWithFlags(&ctx->ev_compute, cudaEventDisableTiming));
@@ -510,6 +515,7 @@ mkv_status mkv_cache_set_len(mkv_cache *h, uint32_t len) {
         return MKV_ERR_CAPACITY;
     }
     c->len = len;
+    c->last_write_pos = 0; // the host wrote the buffers itself
     return MKV_OK;
 }
 
@@ -561,6 +567,7 @@ static mkv_status append_common(Cache *c, int layer0, int n_layers, uint32_t pos
     if (st != MKV_OK) return st;
     c->len = (uint32_t)std::min<uint64_t>(end, shard_end);
     if (c->len < c->shard_first) c->len = c->shard_first;
+    c->last_write_pos = pos;
     return MKV_OK;
 }
 
@@ -595,6 +602,7 @@ mkv_status mkv_truncate(mkv_cache *h, uint32_t new_len, int scrub) {
     const uint32_t old = c->len;
     c->len = std::max(new_len, std::min(c->shard_first, old));
     if (scrub && old > c->len) {
+        c->last_write_pos = 0;
         mkv_status st = use_device(c->ctx);
         if (st != MKV_OK) return st;
         const size_t off = (size_t)(c->len - c->shard_first) * ROW * c->elem;
@@ -828,6 +836,7 @@ mkv_status mkv_restore(mkv_cache *h, uint32_t p, const void *src, size_t bytes) 
     MKV_CUDA(cudaEventRecord(ctx->ev_copy, ctx->copy_stream));
     MKV_CUDA(cudaStreamWaitEvent(ctx->stream, ctx->ev_copy, 0));
     c->len = std::max(r1, std::min(c->shard_first, p));
+    c->last_write_pos = 0;
     return MKV_OK;
 }
 
@@ -916,6 +925,7 @@ mkv_status mkv_dispatch(mkv_cache *h, int layer, const char *op, const uint32_t 
                            c->capacity, pos, ntok, (const float *)in0, (const float *)in0, nullptr, 2u);
         // the V writer is the second of the pair (M/quad.rs:116-117): the rows are now complete
         if (st == MKV_OK) c->len = pos + ntok;
+        c->last_write_pos = 0;
         return st;
     }
     if (is("q_dmx") || is("attn_fd_combine") || is("q_f16")) return MKV_OK; // fused into the attention entry

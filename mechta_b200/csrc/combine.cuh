@@ -8,6 +8,7 @@
 // and fewer of them than there are SMs, so the others always make progress.
 #pragma once
 #include "internal.cuh"
+#include "ptx.cuh"
 
 namespace mkv {
 
@@ -35,11 +36,20 @@ __device__ __forceinline__ void merge_row(const VerifyItem &it, uint32_t r, Fini
     }
     const uint32_t ns = it.nsplit;
     const float2 *ml = reinterpret_cast<const float2 *>(it.part_ml) + (size_t)kvh * ns * 32u + row;
+    const uint32_t grp = tid >> 6, d4 = tid & 63u;
+    const float4 *po = reinterpret_cast<const float4 *>(it.part_o + ((size_t)kvh * ns * 32u + row) * 256u) + d4;
+    // the first round of piece loads goes out together with the (m, l) loads: neither depends on the other
+    float4 x[5];
+#pragma unroll
+    for (int i = 0; i < 5; i++) {
+        const uint32_t s = grp + GROUPS * i;
+        x[i] = s < ns ? __ldcg(po + (size_t)s * 2048u) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     float m = NEG_BIG, l = 0.0f;
     if (tid < ns) {
-        const float2 x = __ldcg(ml + (size_t)tid * 32u);
-        m = x.x;
-        l = x.y;
+        const float2 y = __ldcg(ml + (size_t)tid * 32u);
+        m = y.x;
+        l = y.y;
     }
     float M = m;
 #pragma unroll
@@ -48,10 +58,10 @@ __device__ __forceinline__ void merge_row(const VerifyItem &it, uint32_t r, Fini
     if ((tid & 31u) == 0) sm.red[tid >> 5] = M;
     __syncthreads();
     if (tid < 32) {
-        float x = tid < NW ? sm.red[tid] : NEG_BIG;
+        float y = tid < NW ? sm.red[tid] : NEG_BIG;
 #pragma unroll
-        for (int sh = 16; sh > 0; sh >>= 1) x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, sh));
-        if (tid == 0) sm.M = x;
+        for (int sh = 16; sh > 0; sh >>= 1) y = fmaxf(y, __shfl_xor_sync(0xffffffffu, y, sh));
+        if (tid == 0) sm.M = y;
     }
     __syncthreads();
     M = sm.M;
@@ -63,21 +73,19 @@ __device__ __forceinline__ void merge_row(const VerifyItem &it, uint32_t r, Fini
     if ((tid & 31u) == 0) sm.red[tid >> 5] = t; // the maxima were all read before the barrier above
     __syncthreads();
     if (tid < 32) {
-        float x = tid < NW ? sm.red[tid] : 0.0f;
+        float y = tid < NW ? sm.red[tid] : 0.0f;
 #pragma unroll
-        for (int sh = 16; sh > 0; sh >>= 1) x += __shfl_xor_sync(0xffffffffu, x, sh);
-        if (tid == 0) sm.tot = x;
+        for (int sh = 16; sh > 0; sh >>= 1) y += __shfl_xor_sync(0xffffffffu, y, sh);
+        if (tid == 0) sm.tot = y;
     }
-    const uint32_t grp = tid >> 6, d4 = tid & 63u;
-    const float4 *po = reinterpret_cast<const float4 *>(it.part_o + ((size_t)kvh * ns * 32u + row) * 256u) + d4;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    // rounds of five pieces per group: the five loads of a round are issued before any is used
     for (uint32_t s0 = grp; s0 < ns; s0 += GROUPS * 5u) {
-        float4 x[5];
+        if (s0 != grp) { // later rounds: five loads issued before any is used
 #pragma unroll
-        for (int i = 0; i < 5; i++) {
-            const uint32_t s = s0 + GROUPS * i;
-            x[i] = s < ns ? __ldcg(po + (size_t)s * 2048u) : make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int i = 0; i < 5; i++) {
+                const uint32_t s = s0 + GROUPS * i;
+                x[i] = s < ns ? __ldcg(po + (size_t)s * 2048u) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
         }
 #pragma unroll
         for (int i = 0; i < 5; i++) {
@@ -117,9 +125,8 @@ __device__ __forceinline__ void merge_row(const VerifyItem &it, uint32_t r, Fini
 template <int NT>
 __device__ __forceinline__ void finish_item(const VerifyItem &it, FinishSmem &sm, uint32_t *status) {
     const uint32_t total = 2u * it.nsplit;
-    __threadfence(); // this thread's part of the piece is visible device-wide before the ticket is taken
-    __syncthreads();
-    if (threadIdx.x == 0) sm.ticket = atomicAdd(it.counter, 1u) - it.ticket_base;
+    __syncthreads(); // every thread's part of the piece precedes thread 0's release below
+    if (threadIdx.x == 0) sm.ticket = ptx::atom_add_release_gpu(it.counter, 1u) - it.ticket_base;
     __syncthreads();
     const uint32_t ticket = sm.ticket;
     const uint32_t R = total < 64u ? total : 64u;
@@ -128,8 +135,8 @@ __device__ __forceinline__ void finish_item(const VerifyItem &it, FinishSmem &sm
         // wait until every CTA of the item has published; bounded, in case a CTA never arrives
         const long long t0 = clock64();
         bool ok = true;
-        while (*reinterpret_cast<volatile uint32_t *>(it.counter) - it.ticket_base < total) {
-            __nanosleep(64);
+        while (ptx::ld_acquire_gpu(it.counter) - it.ticket_base < total) {
+            __nanosleep(32);
             if (clock64() - t0 > 4000000000ll) {
                 ok = false;
                 break;
@@ -140,7 +147,6 @@ __device__ __forceinline__ void finish_item(const VerifyItem &it, FinishSmem &sm
     }
     __syncthreads();
     if (!sm.ok) return;
-    __threadfence();
     for (uint32_t r = ticket - (total - R); r < 64u; r += R) merge_row<NT>(it, r, sm);
 }
 

@@ -13,7 +13,7 @@
 namespace mkv {
 
 constexpr int HQ = 16, HKV = 2, D = 256, GROUP = 8, ROW = 512, REC = 258;
-constexpr int TILE = 32;            // keys per verify tile, f16 cache
+constexpr int TILE = 64;            // keys per verify tile, f16 cache (as the reference, M/dmx.rs:53)
 constexpr int PF_TILE = 64;         // keys per prefill tile (as the reference, W/fa_mx.wgsl:27)
 constexpr int TILE32 = 32;          // keys per tile, f32 cache
 constexpr float NEG_BIG = -3.0e38f; // mask value of the reference (W/ops.wgsl:339)
@@ -57,6 +57,7 @@ struct VerifyItem {
     uint32_t partial;   // 1: write the un-normalised record instead of the final output
     uint32_t *counter;  // arrival counter of this item's CTAs (global memory), never reset
     uint32_t ticket_base; // value of the counter before this launch
+    uint32_t safe_below; // keys below this were not written by the kernel launched just before this one
     uint32_t phase;     // measurement only, as the reference's p.f1 phases: 0 = everything, 1 = tile loads only
 };
 
@@ -80,6 +81,7 @@ struct Ctx {
     cudaEvent_t ev_copy = nullptr;    // copy -> compute ordering
     uint32_t *dev_status = nullptr;   // device status word
     uint64_t launches = 0;
+    bool pdl = true; // programmatic dependent launch of the attention kernels (MKV_PDL=0 switches it off)
     // profiling of the attention core kernels
     bool prof = false;
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> prof_events;
@@ -108,6 +110,7 @@ struct Cache {
     uint32_t shard_first = 0;
     bool whole = true;     // holds the whole context (not a sequence shard)
     uint32_t len = 0; // global position after the last valid row
+    uint32_t last_write_pos = 0; // lowest row the most recent writer (append, restore, scrub) touched
     size_t elem = 2;
     size_t buf_bytes = 0;
     std::vector<void *> k, v;

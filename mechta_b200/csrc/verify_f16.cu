@@ -4,14 +4,17 @@
 // Stands in for q_dmx + attn_dmx2 + attn_fd_combine of the reference (M/dmx.rs:19-141, W/ops.wgsl:523-538):
 // same visibility rule (token t at pos + t sees first_pos <= key < pos + 1 + t), same mask value, same
 // un-normalised partial [m, l, O] per piece, one divide at the end. What differs is the machine mapping:
-//  - a CTA owns one KV head and a contiguous run of 32-key tiles; K and V tiles arrive by TMA
-//    (cp.async.bulk.tensor, 128-byte swizzle, no multicast) into a 6-deep ring of 32 KB slots, each filled
+//  - a CTA owns one KV head and a contiguous run of 64-key tiles; K and V tiles arrive by TMA
+//    (cp.async.bulk.tensor, 128-byte swizzle, no multicast) into a 3-deep ring of 64 KB stages, each filled
 //    tile signalled on an mbarrier;
-//  - two groups of 8 warps take alternate tiles, so one group's softmax overlaps the other's tensor work;
-//  - S = Q K^T by mma.m16n8k16 with the Q fragments in registers (f16); softmax with 8 threads per row, max
-//    and sum by warp shuffles, P rounded to f16 (as the reference does) and the row sum taken over the
-//    rounded values; O += P V with warp w of a group owning dims 32w..32w+31, so every V byte is read from
-//    shared memory once per group.
+//  - S = Q K^T: warp w takes keys 8w..8w+7 of the tile for all 32 rows (mma.m16n8k16, Q fragments live in
+//    registers as f16), so every K byte is read from shared memory once;
+//  - softmax: 8 threads per row, max and sum by warp shuffles, P rounded to f16 (as the reference does) and
+//    the row sum taken over the rounded values;
+//  - O += P V: warp w owns dims 32w..32w+31 for all rows, so every V byte is read from shared memory once;
+//  - the CTAs that finish last merge the pieces (combine.cuh), so one launch gives the final output.
+// A variant with two groups of 8 warps taking alternate 32-key tiles was measured slower (76 K against 57 K SM
+// cycles at 65,536 tokens): more barriers per byte and no gain in overlap, since the loop is not compute-bound.
 #include <string.h>
 
 #include "combine.cuh"
@@ -21,23 +24,16 @@
 namespace mkv {
 using namespace ptx;
 
-constexpr int V16_NST = 6;                       // ring depth (three slots per warp group)
-constexpr uint32_t V16_STAGE = 32768;            // K 16 KB + V 16 KB: one tile of 32 keys
-constexpr uint32_t V16_SUB = 4096;               // one [32 keys][64 dims] f16 sub-box
+constexpr int V16_NST = 3;                       // ring depth
+constexpr uint32_t V16_STAGE = 65536;            // K 32 KB + V 32 KB
+constexpr uint32_t V16_SUB = 8192;               // one [64 keys][64 dims] f16 sub-box
 constexpr uint32_t V16_OFF_Q = V16_NST * V16_STAGE;
-constexpr uint32_t V16_S_STRIDE = 36;            // floats per S row (32 + 4 of padding)
-constexpr uint32_t V16_GRP_BYTES = 32 * V16_S_STRIDE * 4 + 32 * 64 + 32 * 4; // S, P, rescale factors of one group
-constexpr uint32_t V16_OFF_GRP = V16_OFF_Q + 32 * 512;
-constexpr uint32_t V16_OFF_ML = V16_OFF_GRP + 2 * V16_GRP_BYTES; // [2 groups][32 rows] (m, l) for the final merge
-constexpr uint32_t V16_OFF_BAR = V16_OFF_ML + 2 * 32 * 8;
-constexpr uint32_t V16_OFF_PRM = V16_OFF_BAR + V16_NST * 8;      // what the TMA issuers need, kept out of registers
-constexpr uint32_t V16_SMEM = V16_OFF_PRM + 32 + 1024;           // + alignment slack
-
-struct IssueParams {
-    const CUtensorMap *kmap, *vmap;
-    int x, y0; // box coordinates of the CTA's first tile
-    volatile uint32_t abort; // set once a bounded wait ran out: later waits are skipped
-};
+constexpr uint32_t V16_OFF_S = V16_OFF_Q + 32 * 512;
+constexpr uint32_t V16_S_STRIDE = 68;            // floats per S row (64 + 4 of padding)
+constexpr uint32_t V16_OFF_P = V16_OFF_S + 32 * V16_S_STRIDE * 4;
+constexpr uint32_t V16_OFF_CF = V16_OFF_P + 32 * 128;
+constexpr uint32_t V16_OFF_BAR = V16_OFF_CF + 32 * 4;
+constexpr uint32_t V16_SMEM = V16_OFF_BAR + V16_NST * 8 + 1024; // + alignment slack
 constexpr long long WAIT_LIMIT = 4000000000ll;   // about two seconds of SM clocks
 
 __device__ __forceinline__ const VerifyItem &pick_item(const VerifyItem *items, int n_items, const VerifyItem &single,
@@ -49,20 +45,7 @@ __device__ __forceinline__ const VerifyItem &pick_item(const VerifyItem *items, 
     return items[lo];
 }
 
-// named barriers of a warp group: 0 = S complete, 1 = P complete, 2 = the tile's slot is released
-__device__ __forceinline__ void group_sync(uint32_t group, uint32_t which) {
-    asm volatile("bar.sync %0, 256;" ::"r"(1u + 3u * group + which) : "memory");
-}
-__device__ __forceinline__ void group_arrive(uint32_t group, uint32_t which) {
-    asm volatile("bar.arrive %0, 256;" ::"r"(1u + 3u * group + which) : "memory");
-}
-// P rows are 64 bytes (32 keys of f16): 16-byte chunk XOR (row / 2) mod 4 keeps ldmatrix conflict-free
-__device__ __forceinline__ uint32_t p_off(uint32_t row, uint32_t chunk) { return row * 64u + ((chunk ^ ((row >> 1) & 3u)) << 4); }
-
-// A CTA = one KV head x a contiguous run of 32-key tiles, worked by two groups of 8 warps that take alternate
-// tiles, each with its own running (m, l, O); while one group is in its softmax the other feeds the tensor
-// pipe. The two states are merged through shared memory at the end, so a CTA still writes one piece.
-__global__ void __launch_bounds__(512, 1)
+__global__ void __launch_bounds__(256, 1)
 verify_f16_kernel(const VerifyItem *__restrict__ items, int n_items, const __grid_constant__ VerifyLaunch single,
                   uint32_t *__restrict__ status) {
     extern __shared__ uint8_t smem_raw[];
@@ -70,52 +53,55 @@ verify_f16_kernel(const VerifyItem *__restrict__ items, int n_items, const __gri
     uint8_t *smem = smem_raw + (smem_base - smem_u32(smem_raw));
 
     const VerifyItem &it = pick_item(items, n_items, single.item, blockIdx.x);
-    const uint32_t tid = threadIdx.x, lane = tid & 31u;
-    const uint32_t group = tid >> 8, gtid = tid & 255u, gw = gtid >> 5; // warp group, thread and warp inside it
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const uint32_t local = blockIdx.x - it.cta_begin;
     if (local >= 2u * it.nsplit) return;
     if (it.phase == 2u) return; // measurement: launch cost alone
+    pdl_launch_dependents();    // the next kernel in the stream may begin its own prologue
     const uint32_t kvh = local & 1u, split = local >> 1;
     const uint32_t t0 = it.tile_begin + split * it.tiles_per_split;
     const uint32_t t1 = min(t0 + it.tiles_per_split, it.tile_end);
     const uint32_t nt = it.phase == 3u ? 0u : t1 - t0; // measurement: prologue and epilogue without tiles
+    // a single launch carries its tensor maps in the parameter space
+    const CUtensorMap *kmap = items ? it.kmap : &single.kmap, *vmap = items ? it.vmap : &single.vmap;
     const uint32_t bar0 = smem_base + V16_OFF_BAR;
-    IssueParams *prm = reinterpret_cast<IssueParams *>(smem + V16_OFF_PRM);
 
     if (tid == 0) {
         for (int s = 0; s < V16_NST; s++) mbar_init(bar0 + 8u * s, 1);
-        prm->kmap = items ? it.kmap : &single.kmap; // a single launch carries its maps in the parameter space
-        prm->vmap = items ? it.vmap : &single.vmap;
-        prm->x = (int)(kvh * 256u);
-        prm->y0 = (int)(t0 * TILE - it.row0);
-        prm->abort = 0;
         fence_barrier_init();
         fence_proxy_async();
     }
     __syncthreads();
 
-    auto issue = [&](uint32_t j) { // one thread of the group that owns tile j: into slot j % NST
+    auto issue = [&](uint32_t j) { // thread 0 only: tile j of this CTA into stage j % NST
         const uint32_t s = j % V16_NST, bar = bar0 + 8u * s;
         const uint32_t dst = smem_base + s * V16_STAGE;
-        const CUtensorMap *kmap = prm->kmap, *vmap = prm->vmap;
-        const int x = prm->x, y = prm->y0 + (int)(j * TILE);
+        const int y = (int)((t0 + j) * TILE - it.row0);
+        const int x = (int)(kvh * 256u);
         mbar_expect_tx(bar, V16_STAGE);
 #pragma unroll
         for (int sb = 0; sb < 4; sb++) tma_load_2d(dst + sb * V16_SUB, kmap, x + 64 * sb, y, bar);
 #pragma unroll
         for (int sb = 0; sb < 4; sb++) tma_load_2d(dst + 4 * V16_SUB + sb * V16_SUB, vmap, x + 64 * sb, y, bar);
     };
-    if (gtid == 0) {
-        for (uint32_t j = group; j < nt && j < (uint32_t)V16_NST; j += 2) issue(j);
-    }
+    // Tiles that lie wholly below `safe_below` hold rows the kernel before this one did not write: their loads
+    // start before that kernel is known to have finished. Everything else (Q, the newest rows, all global
+    // writes) comes after pdl_wait().
+    const uint32_t pre = nt < (uint32_t)V16_NST ? nt : (uint32_t)V16_NST;
+    uint32_t early = 0;
+    if (tid == 0)
+        for (; early < pre && (t0 + early + 1u) * TILE <= it.safe_below; early++) issue(early);
+    pdl_wait();
+    if (tid == 0)
+        for (uint32_t j = early; j < pre; j++) issue(j);
 
     // Q of this KV head to shared memory as f16: row = tok * 8 + head % 8 (the order of q_dmx, M/dmx.rs:128-138),
     // rows of tokens >= ntok zero; 16-byte chunks swizzled inside each 128-byte group
     {
         uint8_t *qs = smem + V16_OFF_Q;
 #pragma unroll
-        for (int i = 0; i < 2; i++) {
-            const uint32_t idx = tid + 512u * i; // 32 rows x 32 chunks of 8 dims
+        for (int i = 0; i < 4; i++) {
+            const uint32_t idx = tid + 256u * i; // 32 rows x 32 chunks of 8 dims
             const uint32_t row = idx >> 5, chunk = idx & 31u;
             uint4 w = make_uint4(0, 0, 0, 0);
             const uint32_t tok = row >> 3;
@@ -136,22 +122,22 @@ verify_f16_kernel(const VerifyItem *__restrict__ items, int n_items, const __gri
     }
     __syncthreads();
 
-    // S = Q K^T: warp gw of a group takes the 16-row tile mt = gw & 1 and keys 8 kq .. 8 kq + 7, kq = gw >> 1.
-    // Its A fragments of Q (16 rows x 256 dims) live in registers for the whole kernel.
-    const uint32_t mt = gw & 1u, kq = gw >> 1;
-    uint32_t qf[16][4];
+    // A fragments of Q for both 16-row tiles and all 16 k-steps
+    uint32_t qf[2][16][4];
     {
         const uint32_t qs = smem_base + V16_OFF_Q;
 #pragma unroll
-        for (int ks = 0; ks < 16; ks++) {
-            const uint32_t row = mt * 16u + (lane & 7u) + 8u * ((lane >> 3) & 1u);
-            const uint32_t chunk = 2u * ks + (lane >> 4);
-            const uint32_t pc = (chunk & ~7u) | ((chunk ^ row) & 7u);
-            ldmatrix_x4(qf[ks], qs + row * 512u + pc * 16u);
-        }
+        for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+            for (int ks = 0; ks < 16; ks++) {
+                const uint32_t row = mt * 16u + (lane & 7u) + 8u * ((lane >> 3) & 1u);
+                const uint32_t chunk = 2u * ks + (lane >> 4);
+                const uint32_t pc = (chunk & ~7u) | ((chunk ^ row) & 7u);
+                ldmatrix_x4(qf[mt][ks], qs + row * 512u + pc * 16u);
+            }
     }
 
-    float o[2][4][4]; // O += P V: warp gw owns dims 32 gw .. 32 gw + 31 of all 32 rows
+    float o[2][4][4];
 #pragma unroll
     for (int a = 0; a < 2; a++)
 #pragma unroll
@@ -159,58 +145,69 @@ verify_f16_kernel(const VerifyItem *__restrict__ items, int n_items, const __gri
 #pragma unroll
             for (int c = 0; c < 4; c++) o[a][b][c] = 0.0f;
 
-    // softmax ownership inside the group: 8 threads per row, 4 keys each
-    const uint32_t srow = gtid >> 3, seg = gtid & 7u;
-    const uint32_t vis = min(it.pos + 1u + (srow >> 3), it.key_hi);
+    // softmax ownership: 8 threads per row
+    const uint32_t srow = tid >> 3, seg = tid & 7u;
+    const uint32_t stok = srow >> 3;
+    const uint32_t vis = min(it.pos + 1u + stok, it.key_hi);
     const uint32_t klo = max(it.first_pos, it.key_lo);
     float m_run = NEG_BIG, l_run = 0.0f;
-    uint8_t *gmem = smem + V16_OFF_GRP + group * V16_GRP_BYTES;
-    float *S = reinterpret_cast<float *>(gmem);
-    uint8_t *P = gmem + 32 * V16_S_STRIDE * 4;
-    float *cfs = reinterpret_cast<float *>(P + 32 * 64);
-    const uint32_t Pbase = smem_base + V16_OFF_GRP + group * V16_GRP_BYTES + 32 * V16_S_STRIDE * 4;
+    float *S = reinterpret_cast<float *>(smem + V16_OFF_S);
+    float *cfs = reinterpret_cast<float *>(smem + V16_OFF_CF);
+    const uint32_t Pbase = smem_base + V16_OFF_P;
+    bool aborted = false;
     const uint32_t g = lane >> 2, qd = lane & 3u;
 
-    for (uint32_t j = group; j < nt; j += 2) {
+    for (uint32_t j = 0; j < nt; j++) {
         const uint32_t s = j % V16_NST;
-        if (lane == 0 && !prm->abort && !mbar_wait_bounded(bar0 + 8u * s, (j / V16_NST) & 1u, WAIT_LIMIT)) {
-            prm->abort = 1; // one lane per warp polls, so that waiting warps leave the shared-memory pipe alone
+        if (!aborted && !mbar_wait_bounded(bar0 + 8u * s, (j / V16_NST) & 1u, WAIT_LIMIT)) {
+            aborted = true;
             atomicOr(status, DEV_ERR_WAIT_TIMEOUT);
         }
-        __syncwarp();
         const uint32_t Kb = smem_base + s * V16_STAGE, Vb = Kb + 4 * V16_SUB;
         if (it.phase == 1u) { // measurement: stream the tiles only
-            group_sync(group, 0);
-            if (gtid == 0 && j + V16_NST < nt) issue(j + V16_NST);
+            __syncthreads();
+            if (tid == 0 && j >= 1 && j - 1 + V16_NST < nt) issue(j - 1 + V16_NST);
             continue;
         }
 
-        // ---- S(16 x 8) = Q K^T ----
+        // ---- S = Q K^T for keys 8 warp .. 8 warp + 7 ----
+        float sc[2][4];
+#pragma unroll
+        for (int a = 0; a < 2; a++)
+#pragma unroll
+            for (int c = 0; c < 4; c++) sc[a][c] = 0.0f;
         {
-            float sa[4] = {0.f, 0.f, 0.f, 0.f};
-            const uint32_t krow = kq * 8u + (lane & 7u);
+            const uint32_t krow = warp * 8u + (lane & 7u);
             const uint32_t jm = lane >> 3; // which 8x8 matrix this lane addresses
 #pragma unroll
             for (int kp = 0; kp < 8; kp++) { // 32 dims per step
                 uint32_t kb[4];
                 ldmatrix_x4(kb, Kb + (kp >> 1) * V16_SUB + swz128(krow, (kp & 1) * 4u + jm));
-                mma_f16(sa, qf[2 * kp], kb[0], kb[1]);
-                mma_f16(sa, qf[2 * kp + 1], kb[2], kb[3]);
+                mma_f16(sc[0], qf[0][2 * kp], kb[0], kb[1]);
+                mma_f16(sc[1], qf[1][2 * kp], kb[0], kb[1]);
+                mma_f16(sc[0], qf[0][2 * kp + 1], kb[2], kb[3]);
+                mma_f16(sc[1], qf[1][2 * kp + 1], kb[2], kb[3]);
             }
-            float *r0 = S + (mt * 16u + g) * V16_S_STRIDE + kq * 8u + 2u * qd;
-            *reinterpret_cast<float2 *>(r0) = make_float2(sa[0], sa[1]);
-            *reinterpret_cast<float2 *>(r0 + 8 * V16_S_STRIDE) = make_float2(sa[2], sa[3]);
         }
-        group_sync(group, 0); // S complete; every warp of the group is past the P V of its previous tile
+#pragma unroll
+        for (int mt = 0; mt < 2; mt++) {
+            float *r0 = S + (mt * 16u + g) * V16_S_STRIDE + warp * 8u + 2u * qd;
+            *reinterpret_cast<float2 *>(r0) = make_float2(sc[mt][0], sc[mt][1]);
+            *reinterpret_cast<float2 *>(r0 + 8 * V16_S_STRIDE) = make_float2(sc[mt][2], sc[mt][3]);
+        }
+        __syncthreads(); // S complete; every warp is past the P V of the previous tile
 
-        // ---- softmax of row srow over this tile's 32 keys ----
+        if (tid == 0 && j >= 1 && j - 1 + V16_NST < nt) issue(j - 1 + V16_NST); // refill the stage just released
+
+        // ---- softmax of row srow over this tile's 64 keys ----
         {
-            const float4 a = *reinterpret_cast<const float4 *>(S + srow * V16_S_STRIDE + seg * 4u);
-            float v[4] = {a.x, a.y, a.z, a.w};
-            const uint32_t key0 = (t0 + j) * TILE + seg * 4u;
+            const float4 a = *reinterpret_cast<const float4 *>(S + srow * V16_S_STRIDE + seg * 8u);
+            const float4 b = *reinterpret_cast<const float4 *>(S + srow * V16_S_STRIDE + seg * 8u + 4u);
+            float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+            const uint32_t key0 = (t0 + j) * TILE + seg * 8u;
             float mt_ = NEG_BIG;
 #pragma unroll
-            for (int c = 0; c < 4; c++) {
+            for (int c = 0; c < 8; c++) {
                 const uint32_t key = key0 + c;
                 v[c] = (key >= klo && key < vis) ? v[c] * SCALE : NEG_BIG; // scale, then mask (M/dmx.rs:71)
                 mt_ = fmaxf(mt_, v[c]);
@@ -219,26 +216,29 @@ verify_f16_kernel(const VerifyItem *__restrict__ items, int n_items, const __gri
             mt_ = fmaxf(mt_, __shfl_xor_sync(0xffffffffu, mt_, 2));
             mt_ = fmaxf(mt_, __shfl_xor_sync(0xffffffffu, mt_, 4));
             const float m_new = fmaxf(m_run, mt_);
-            const float w0 = v[0] > NEG_TEST ? __expf(v[0] - m_new) : 0.0f;
-            const float w1 = v[1] > NEG_TEST ? __expf(v[1] - m_new) : 0.0f;
-            const float w2 = v[2] > NEG_TEST ? __expf(v[2] - m_new) : 0.0f;
-            const float w3 = v[3] > NEG_TEST ? __expf(v[3] - m_new) : 0.0f;
-            const __half2 h01 = __floats2half2_rn(w0, w1), h23 = __floats2half2_rn(w2, w3);
-            const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
-            float sum = (f01.x + f01.y) + (f23.x + f23.y); // the sum of the rounded weights, as M/dmx.rs:84
+            float sum = 0.0f;
+            uint32_t pk[4];
+#pragma unroll
+            for (int c = 0; c < 8; c += 2) {
+                const float w0 = v[c] > NEG_TEST ? __expf(v[c] - m_new) : 0.0f;
+                const float w1 = v[c + 1] > NEG_TEST ? __expf(v[c + 1] - m_new) : 0.0f;
+                const __half2 h = __floats2half2_rn(w0, w1);
+                const float2 f = __half22float2(h);
+                sum += f.x + f.y;
+                pk[c >> 1] = *reinterpret_cast<const uint32_t *>(&h);
+            }
             sum += __shfl_xor_sync(0xffffffffu, sum, 1);
             sum += __shfl_xor_sync(0xffffffffu, sum, 2);
             sum += __shfl_xor_sync(0xffffffffu, sum, 4);
             const float cf = m_run > NEG_TEST ? __expf(m_run - m_new) : 0.0f;
             l_run = l_run * cf + sum;
             m_run = m_new;
-            *reinterpret_cast<uint2 *>(P + p_off(srow, seg >> 1) + (seg & 1u) * 8u) =
-                make_uint2(*reinterpret_cast<const uint32_t *>(&h01), *reinterpret_cast<const uint32_t *>(&h23));
+            *reinterpret_cast<uint4 *>(smem + V16_OFF_P + swz128(srow, seg)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
             if (seg == 0) cfs[srow] = cf;
         }
-        group_sync(group, 1); // P and the rescale factors are visible
+        __syncthreads(); // P and the rescale factors are visible
 
-        // ---- O = O * cf + P V for dims 32 gw .. 32 gw + 31 ----
+        // ---- O = O * cf + P V for dims 32 warp .. 32 warp + 31 ----
         {
             const float c0 = cfs[g], c1 = cfs[g + 8], c2 = cfs[16 + g], c3 = cfs[24 + g];
 #pragma unroll
@@ -246,16 +246,16 @@ verify_f16_kernel(const VerifyItem *__restrict__ items, int n_items, const __gri
                 o[0][n][0] *= c0; o[0][n][1] *= c0; o[0][n][2] *= c1; o[0][n][3] *= c1;
                 o[1][n][0] *= c2; o[1][n][1] *= c2; o[1][n][2] *= c3; o[1][n][3] *= c3;
             }
-            const uint32_t Vsub = Vb + (gw >> 1) * V16_SUB;
-            const uint32_t cb = (gw & 1u) * 4u;
+            const uint32_t Vsub = Vb + (warp >> 1) * V16_SUB;
+            const uint32_t cb = (warp & 1u) * 4u;
             const uint32_t jm = lane >> 3;
 #pragma unroll
-            for (int ks = 0; ks < 2; ks++) { // 16 keys per step
+            for (int ks = 0; ks < 4; ks++) { // 16 keys per step
                 uint32_t pa[2][4];
 #pragma unroll
-                for (int m2 = 0; m2 < 2; m2++) {
-                    const uint32_t row = m2 * 16u + (lane & 7u) + 8u * ((lane >> 3) & 1u);
-                    ldmatrix_x4(pa[m2], Pbase + p_off(row, 2u * ks + (lane >> 4)));
+                for (int mt = 0; mt < 2; mt++) {
+                    const uint32_t row = mt * 16u + (lane & 7u) + 8u * ((lane >> 3) & 1u);
+                    ldmatrix_x4(pa[mt], Pbase + swz128(row, 2u * ks + (lane >> 4)));
                 }
 #pragma unroll
                 for (int np = 0; np < 2; np++) { // two 8-dim tiles per load
@@ -269,56 +269,27 @@ verify_f16_kernel(const VerifyItem *__restrict__ items, int n_items, const __gri
                 }
             }
         }
-        // the slot is free once all 8 warps are done with it: warp 0 waits for the others' arrival and
-        // refills it at once with the tile three of the group's turns ahead
-        if (gw != 0) group_arrive(group, 2);
-        else {
-            group_sync(group, 2);
-            if (lane == 0 && j + V16_NST < nt) issue(j + V16_NST);
-        }
     }
 
-    // ---- merge the two groups' states through shared memory, then write the CTA's piece ----
-    float2 *mls = reinterpret_cast<float2 *>(smem + V16_OFF_ML); // [group][row]
-    if (seg == 0) mls[group * 32u + srow] = make_float2(m_run, l_run);
-    __syncthreads(); // every tile is consumed: the ring is free to hold group 1's O
-    float *xo = reinterpret_cast<float *>(smem); // [32 rows][256 + 8]: padded against bank conflicts
-    constexpr uint32_t XS = 264;
-    if (group == 1) {
-#pragma unroll
-        for (int m2 = 0; m2 < 2; m2++)
-#pragma unroll
-            for (int n = 0; n < 4; n++) {
-                const uint32_t row = m2 * 16u + g, col = gw * 32u + n * 8u + 2u * qd;
-                *reinterpret_cast<float2 *>(xo + row * XS + col) = make_float2(o[m2][n][0], o[m2][n][1]);
-                *reinterpret_cast<float2 *>(xo + (row + 8u) * XS + col) = make_float2(o[m2][n][2], o[m2][n][3]);
-            }
+    // ---- the piece's partial: [m, l] per row and O[32][256] ----
+    const size_t piece = (size_t)kvh * it.nsplit + split;
+    if (seg == 0) {
+        float2 *ml = reinterpret_cast<float2 *>(it.part_ml) + piece * 32u + srow;
+        *ml = make_float2(m_run, l_run);
     }
-    __syncthreads();
-    if (group == 0) {
-        const size_t piece = (size_t)kvh * it.nsplit + split;
+    {
         float *po = it.part_o + piece * 32u * 256u;
 #pragma unroll
-        for (int m2 = 0; m2 < 2; m2++)
+        for (int mt = 0; mt < 2; mt++)
 #pragma unroll
-            for (int h = 0; h < 2; h++) {
-                const uint32_t row = m2 * 16u + g + 8u * h;
-                const float2 a = mls[row], b = mls[32u + row];
-                const float M = fmaxf(a.x, b.x);
-                const float ea = __expf(a.x - M), eb = __expf(b.x - M); // both -3e38: 1 and 1, with l = 0 and O = 0
-#pragma unroll
-                for (int n = 0; n < 4; n++) {
-                    const uint32_t col = gw * 32u + n * 8u + 2u * qd;
-                    const float2 x = *reinterpret_cast<const float2 *>(xo + row * XS + col);
-                    *reinterpret_cast<float2 *>(po + (size_t)row * 256u + col) =
-                        make_float2(o[m2][n][2 * h] * ea + x.x * eb, o[m2][n][2 * h + 1] * ea + x.y * eb);
-                }
-                if (gw == 0 && qd == 0)
-                    reinterpret_cast<float2 *>(it.part_ml)[piece * 32u + row] = make_float2(M, a.y * ea + b.y * eb);
+            for (int n = 0; n < 4; n++) {
+                const uint32_t row = mt * 16u + g, col = warp * 32u + n * 8u + 2u * qd;
+                *reinterpret_cast<float2 *>(po + (size_t)row * 256u + col) = make_float2(o[mt][n][0], o[mt][n][1]);
+                *reinterpret_cast<float2 *>(po + (size_t)(row + 8u) * 256u + col) = make_float2(o[mt][n][2], o[mt][n][3]);
             }
     }
-    // the CTAs that finish last merge the pieces (scratch in the ring, beyond group 1's O)
-    finish_item<512>(it, *reinterpret_cast<FinishSmem *>(smem + 65536), status);
+    // the CTAs that finish last merge the pieces (scratch in the ring, which is drained by now)
+    finish_item<256>(it, *reinterpret_cast<FinishSmem *>(smem), status);
 }
 
 // Log-sum-exp merge of the pieces of one row: attn_fd_combine's arithmetic (W/ops.wgsl:529-537) over this
@@ -515,9 +486,20 @@ mkv_status launch_verify(Ctx *ctx, mkv_fmt fmt, VerifyItem *items_host, int n, b
     }
     if (total > 0) {
         if (fmt == MKV_F16) {
-            verify_f16_kernel<<<total, 512, V16_SMEM, ctx->stream>>>(items_dev, n, single, ctx->dev_status);
+            // programmatic dependent launch: this kernel's prologue and first tile loads may overlap the tail
+            // of the kernel before it in the stream (see pdl_wait in the kernel)
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(total);
+            cfg.blockDim = dim3(256);
+            cfg.dynamicSmemBytes = V16_SMEM;
+            cfg.stream = ctx->stream;
+            cudaLaunchAttribute at[1];
+            at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            at[0].val.programmaticStreamSerializationAllowed = ctx->pdl ? 1 : 0;
+            cfg.attrs = at;
+            cfg.numAttrs = 1;
+            MKV_CUDA(cudaLaunchKernelEx(&cfg, verify_f16_kernel, items_dev, n, single, ctx->dev_status));
             ctx->launches++;
-            MKV_CUDA(cudaGetLastError());
         } else {
             mkv_status st = launch_verify_f32(ctx, items_dev, n, single, total);
             if (st != MKV_OK) return st;
