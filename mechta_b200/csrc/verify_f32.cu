@@ -45,6 +45,7 @@ verify_f32_kernel(const VerifyItem *__restrict__ items, int n_items, const __gri
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const uint32_t local = blockIdx.x - it.cta_begin;
     if (local >= 2u * it.nsplit) return;
+    pdl_launch_dependents(); // the next kernel in the stream may begin its own prologue
     const uint32_t kvh = local & 1u, split = local >> 1;
     const uint32_t t0 = it.tile_begin + split * it.tiles_per_split;
     const uint32_t t1 = min(t0 + it.tiles_per_split, it.tile_end);
@@ -71,10 +72,15 @@ verify_f32_kernel(const VerifyItem *__restrict__ items, int n_items, const __gri
 #pragma unroll
         for (int sb = 0; sb < 8; sb++) tma_load_2d(dst + 8 * V32_SUB + sb * V32_SUB, vmap, x + 32 * sb, y, bar);
     };
-    if (tid == 0) {
-        const uint32_t pre = nt < (uint32_t)V32_NST ? nt : (uint32_t)V32_NST;
-        for (uint32_t j = 0; j < pre; j++) issue(j);
-    }
+    // tiles wholly below `safe_below` were not written by the kernel before this one: their loads start before
+    // that kernel is known to have finished; Q, the newest rows and all global writes come after pdl_wait()
+    const uint32_t pre = nt < (uint32_t)V32_NST ? nt : (uint32_t)V32_NST;
+    uint32_t early = 0;
+    if (tid == 0)
+        for (; early < pre && (t0 + early + 1u) * TILE32 <= it.safe_below; early++) issue(early);
+    pdl_wait();
+    if (tid == 0)
+        for (uint32_t j = early; j < pre; j++) issue(j);
 
     // Q rows of this KV head: [row = tok * 8 + head % 8][256] f32, rows of tokens >= ntok zero
     float *Q = reinterpret_cast<float *>(smem + V32_OFF_Q);
@@ -215,9 +221,18 @@ mkv_status verify_f32_setup_device() {
 }
 
 mkv_status launch_verify_f32(Ctx *ctx, const VerifyItem *items_dev, int n, const VerifyLaunch &single, uint32_t total_ctas) {
-    verify_f32_kernel<<<total_ctas, 256, V32_SMEM, ctx->stream>>>(items_dev, n, single, ctx->dev_status);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(total_ctas);
+    cfg.blockDim = dim3(256);
+    cfg.dynamicSmemBytes = V32_SMEM;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = ctx->pdl ? 1 : 0;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    MKV_CUDA(cudaLaunchKernelEx(&cfg, verify_f32_kernel, items_dev, n, single, ctx->dev_status));
     ctx->launches++;
-    MKV_CUDA(cudaGetLastError());
     return MKV_OK;
 }
 

@@ -22,6 +22,27 @@ def shard_range(context: int, world: int, rank: int) -> tuple[int, int]:
     return rank * per, per
 
 
+def gather_records(rec: torch.Tensor, recs: torch.Tensor, group=None) -> None:
+    """All-gather of the per-rank records [64][258] into recs [world][64][258] (rank order = shard order)."""
+    dist.all_gather_into_tensor(recs.view(-1), rec.view(-1), group=group)
+
+
+class ShardPlan:
+    """Which rows a rank holds and who owns a position; no device needed."""
+
+    def __init__(self, context: int, world: int, rank: int):
+        self.context, self.world, self.rank = kv.check_ctx(context), world, rank
+        self.first, self.per = shard_range(self.context, world, rank)
+
+    def owner_of(self, pos: int) -> int:
+        return min(pos // self.per, self.world - 1)
+
+    def rows_of_append(self, pos: int, ntok: int) -> range:
+        """The positions of an append at `pos` that this rank stores."""
+        lo, hi = max(pos, self.first), min(pos + ntok, self.first + self.per)
+        return range(lo, max(lo, hi))
+
+
 class ShardedKvCache:
     """This rank's shard of a sequence-sharded KV cache plus the exchange step of its attention.
 
@@ -34,7 +55,8 @@ class ShardedKvCache:
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
-        self.first, self.per = shard_range(kv.check_ctx(context), self.world, self.rank)
+        self.plan = ShardPlan(context, self.world, self.rank)
+        self.first, self.per = self.plan.first, self.plan.per
         self.ctx = ctx
         self.cache = kv.KvCache(ctx, fmt, n_layers, context, shard_first=self.first,
                                 shard_tokens=self.per if self.world > 1 else 0)
@@ -43,7 +65,7 @@ class ShardedKvCache:
         self.rec = torch.empty(64, 258, device=dev)
 
     def owner_of(self, pos: int) -> int:
-        return min(pos // self.per, self.world - 1)
+        return self.plan.owner_of(pos)
 
     def append_layers(self, pos, k, v, tab):
         """Every rank calls this; only rows inside the rank's shard are written (appends go to the owner)."""
@@ -61,7 +83,7 @@ class ShardedKvCache:
             self.cache.attn_verify(layer, first_pos, pos, q, out)
             return
         self.cache.attn_verify_partial(layer, first_pos, pos, q, self.rec)
-        dist.all_gather_into_tensor(self.recs, self.rec, group=self.group)
+        gather_records(self.rec, self.recs, self.group)
         self.ctx.combine_shards(self.recs, q.shape[0], out)
 
     def close(self):
