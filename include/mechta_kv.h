@@ -141,6 +141,23 @@ mkv_status mkv_attn_verify_partial(mkv_cache *c, int layer, uint32_t first_pos, 
 mkv_status mkv_combine_shards(mkv_ctx *ctx, const float *recs_dev /*[n_shards][64][258]*/, int n_shards,
                               uint32_t ntok, float *out_dev /*[ntok][16][256]*/);
 
+/* Verify attention without any allocation by the library. No counterpart in the reference (which allocates
+ * all its buffers once at start-up, M/engine.rs:204-252): this is for hosts that cannot let a library call
+ * cudaMalloc — all device memory already belongs to their own planner, or the call comes from a place where
+ * allocating is not allowed. Same result as mkv_attn_verify on an f16 cache, but the caller owns the cache:
+ * k_dev / v_dev are f16 buffers [capacity_tokens][2][256] (16-byte aligned), q_dev / out_dev f32 [ntok][16][256],
+ * `stream` a cudaStream_t (NULL = legacy default stream), `device` the CUDA device all of them live on.
+ * The split-K pieces go to a fixed array inside the library image (5,284,096 bytes on every GPU that loads
+ * the library, held until the process exits) with room for 160 pieces = one CTA per SM up to 160 SMs; a launch
+ * that would need more fails with MKV_ERR_CAPACITY. The first call on a device looks up the array's device
+ * address, opts the kernel into its shared memory and clears the header (a blocking cudaMemset): make that
+ * first call before any stream capture begins. All calls share the array, which keeps the previous call's
+ * contents (the counter is cleared on the stream before each launch): calls whose kernels may overlap on the
+ * GPU, e.g. on two streams, race on it. Calls cudaMalloc / cudaFree nowhere. */
+mkv_status mkv_attn_verify_static(int device, void *stream, const void *k_dev, const void *v_dev,
+                                  uint32_t capacity_tokens, uint32_t first_pos, uint32_t pos, uint32_t ntok,
+                                  const float *q_dev, float *out_dev);
+
 /* Ragged batch: n independent (cache, layer, position) verify steps in one launch pair; every cache must
  * belong to `ctx`. Each item behaves exactly as one mkv_attn_verify call. */
 typedef struct {

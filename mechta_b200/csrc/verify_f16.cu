@@ -515,6 +515,142 @@ mkv_status launch_verify(Ctx *ctx, mkv_fmt fmt, VerifyItem *items_host, int n, b
     return MKV_OK;
 }
 
+// ---- verify attention for callers that must not allocate ------------------------------------------------------
+//
+// Some hosts hand all device memory to their own planner at start-up, or call from a region where allocation
+// is forbidden (a latency-critical serving loop, a callback, a driver-level hook), and so cannot let this
+// library call cudaMalloc for its split-K pieces. For them the pieces, the arrival counter and the status word
+// of one verify launch live in the array below, which is part of the library image: every GPU that loads the
+// library holds these 5,284,096 bytes until the process exits, whether or not the entry point is used.
+// It holds at most MKV_STATIC_MAX_PIECES pieces (two per CTA pair of KV heads), which covers one CTA per SM on
+// a B200 (148). All calls share it and it keeps the last call's contents: calls whose kernels overlap on the
+// GPU (different streams) race on it.
+constexpr uint32_t STATIC_MAX_PIECES = 160;
+constexpr size_t STATIC_HDR = 256; // counter at byte 0, status word at byte 64
+constexpr size_t STATIC_ML = (size_t)STATIC_MAX_PIECES * 32 * 2 * sizeof(float);
+constexpr size_t STATIC_O = (size_t)STATIC_MAX_PIECES * 32 * 256 * sizeof(float);
+static __device__ __align__(256) unsigned char g_static_scratch[STATIC_HDR + STATIC_ML + STATIC_O];
+
+namespace {
+constexpr int STATIC_MAX_DEVICES = 64;
+struct StaticDevice {
+    bool ready = false;
+    unsigned char *scratch = nullptr; // device address of g_static_scratch on this device
+    int sm_count = 0;
+};
+StaticDevice g_static_dev[STATIC_MAX_DEVICES];
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// Once per device, with that device current: the device address of the array (in host code its name is only a
+// stand-in, not an address a kernel can use), the shared-memory opt-in of the kernel, the SM count.
+mkv_status static_setup(int device) {
+    StaticDevice &d = g_static_dev[device];
+    if (d.ready) return MKV_OK;
+    void *p = nullptr;
+    MKV_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+    MKV_CUDA(cudaFuncSetAttribute(verify_f16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)V16_SMEM));
+    MKV_CUDA(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, device));
+    MKV_CUDA(cudaMemset(p, 0, STATIC_HDR)); // counter and status start at zero
+    d.scratch = static_cast<unsigned char *>(p);
+    d.ready = true;
+    return MKV_OK;
+}
+} // namespace
+
+} // namespace mkv
+
+extern "C" mkv_status mkv_attn_verify_static(int device, void *stream, const void *k_dev, const void *v_dev,
+                                             uint32_t capacity_tokens, uint32_t first_pos, uint32_t pos, uint32_t ntok,
+                                             const float *q_dev, float *out_dev) {
+    using namespace mkv;
+    if (device < 0 || device >= STATIC_MAX_DEVICES || !k_dev || !v_dev || !q_dev || !out_dev) {
+        set_error("mkv_attn_verify_static: null pointer or device outside [0, %d)", STATIC_MAX_DEVICES);
+        return MKV_ERR_INVALID;
+    }
+    if (ntok < 1 || ntok > MKV_MAX_VERIFY || first_pos > pos) {
+        set_error("mkv_attn_verify_static: ntok %u outside [1, %d] or first_pos %u > pos %u", ntok, MKV_MAX_VERIFY, first_pos, pos);
+        return MKV_ERR_INVALID;
+    }
+    if (((uintptr_t)k_dev & 15u) || ((uintptr_t)v_dev & 15u) || ((uintptr_t)q_dev & 15u) || ((uintptr_t)out_dev & 15u)) {
+        set_error("mkv_attn_verify_static: k, v, q and out must be 16-byte aligned");
+        return MKV_ERR_INVALID;
+    }
+    if (capacity_tokens == 0 || capacity_tokens > (uint32_t)MKV_CTX_MAX || (uint64_t)pos + ntok > capacity_tokens) {
+        set_error("mkv_attn_verify_static: rows [%u, %u) outside a cache of %u rows (at most %d)", first_pos, pos + ntok,
+                  capacity_tokens, MKV_CTX_MAX);
+        return MKV_ERR_CAPACITY;
+    }
+    MKV_CUDA(cudaSetDevice(device));
+    mkv_status st = static_setup(device);
+    if (st != MKV_OK) return st;
+    const StaticDevice &d = g_static_dev[device];
+
+    // the same plan as mkv_attn_verify: contiguous runs of 64-key tiles, one CTA per SM at most
+    VerifyLaunch L;
+    memset(&L, 0, sizeof L);
+    VerifyItem &it = L.item;
+    it.q = q_dev;
+    it.out = out_dev;
+    it.first_pos = first_pos;
+    it.pos = pos;
+    it.ntok = ntok;
+    it.key_hi = capacity_tokens;
+    it.tile_begin = first_pos / TILE;
+    it.tile_end = (pos + ntok + TILE - 1) / TILE;
+    const uint32_t tiles = it.tile_end - it.tile_begin;
+    const uint32_t budget = (uint32_t)d.sm_count;
+    uint32_t tps = (2u * tiles + budget - 1) / budget;
+    if (tps == 0) tps = 1;
+    while (2u * ((tiles + tps - 1) / tps) > budget && 2u * ((tiles + tps - 1) / tps) > 2u) tps++;
+    it.tiles_per_split = tps;
+    it.nsplit = (tiles + tps - 1) / tps;
+    if (2u * it.nsplit > STATIC_MAX_PIECES) {
+        set_error("mkv_attn_verify_static: this launch needs %u split-K pieces, the static scratch holds %u", 2u * it.nsplit,
+                  STATIC_MAX_PIECES);
+        return MKV_ERR_CAPACITY;
+    }
+    it.counter = reinterpret_cast<uint32_t *>(d.scratch);
+    it.ticket_base = 0;
+    it.part_ml = reinterpret_cast<float *>(d.scratch + STATIC_HDR);
+    it.part_o = reinterpret_cast<float *>(d.scratch + STATIC_HDR + STATIC_ML);
+
+    static EncodeTiledFn enc = nullptr;
+    if (!enc) {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess) {
+            set_error("cuTensorMapEncodeTiled is not available from the driver");
+            return MKV_ERR_CUDA;
+        }
+        enc = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    const cuuint64_t dims[2] = {512, capacity_tokens};
+    const cuuint64_t strides[1] = {1024};
+    const cuuint32_t box[2] = {64, (cuuint32_t)TILE};
+    const cuuint32_t estr[2] = {1, 1};
+    for (int i = 0; i < 2; i++) {
+        const CUresult r = enc(i ? &L.vmap : &L.kmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(i ? v_dev : k_dev),
+                               dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) {
+            set_error("cuTensorMapEncodeTiled failed with %d", (int)r);
+            return MKV_ERR_CUDA;
+        }
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // the arrival counter must start at zero: the array still holds the last call's count
+    MKV_CUDA(cudaMemsetAsync(d.scratch, 0, sizeof(uint32_t), s));
+    verify_f16_kernel<<<2u * it.nsplit, 256, V16_SMEM, s>>>(nullptr, 1, L, reinterpret_cast<uint32_t *>(d.scratch + 64));
+    MKV_CUDA(cudaGetLastError());
+    return MKV_OK;
+}
+
+namespace mkv {
+
 // Chooses tiles_per_split so that all items together fill the SMs in one wave (one CTA per SM), and lays
 // the items out in the flattened grid. Items must have tile_begin / tile_end set.
 void plan_items(Ctx *ctx, VerifyItem *items, int n) {
