@@ -120,21 +120,28 @@ verify_f32_kernel(const VerifyItem *__restrict__ items, int n_items, const __gri
 
         // ---- scores of key `lane` against rows 4 warp .. 4 warp + 3 ----
         if (4u * warp < nrow) {
-            float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+            // 16 independent accumulators (4 rows x 4 lanes of the 16-byte chunk): no FMA waits on the one before
+            float d[4][4];
+#pragma unroll
+            for (int r = 0; r < 4; r++)
+#pragma unroll
+                for (int c = 0; c < 4; c++) d[r][c] = 0.f;
             const float *q0 = Q + (4u * warp) * 256u;
 #pragma unroll 8
             for (uint32_t c = 0; c < 64u; c++) {
                 const float4 k4 = *reinterpret_cast<const float4 *>(Kt + (c >> 3) * V32_SUB + swz128(lane, c & 7u));
-                const float4 a = *reinterpret_cast<const float4 *>(q0 + c * 4u);
-                const float4 b = *reinterpret_cast<const float4 *>(q0 + 256u + c * 4u);
-                const float4 e = *reinterpret_cast<const float4 *>(q0 + 512u + c * 4u);
-                const float4 f = *reinterpret_cast<const float4 *>(q0 + 768u + c * 4u);
-                d0 = fmaf(a.x, k4.x, d0); d0 = fmaf(a.y, k4.y, d0); d0 = fmaf(a.z, k4.z, d0); d0 = fmaf(a.w, k4.w, d0);
-                d1 = fmaf(b.x, k4.x, d1); d1 = fmaf(b.y, k4.y, d1); d1 = fmaf(b.z, k4.z, d1); d1 = fmaf(b.w, k4.w, d1);
-                d2 = fmaf(e.x, k4.x, d2); d2 = fmaf(e.y, k4.y, d2); d2 = fmaf(e.z, k4.z, d2); d2 = fmaf(e.w, k4.w, d2);
-                d3 = fmaf(f.x, k4.x, d3); d3 = fmaf(f.y, k4.y, d3); d3 = fmaf(f.z, k4.z, d3); d3 = fmaf(f.w, k4.w, d3);
+#pragma unroll
+                for (int r = 0; r < 4; r++) {
+                    const float4 a = *reinterpret_cast<const float4 *>(q0 + r * 256u + c * 4u);
+                    d[r][0] = fmaf(a.x, k4.x, d[r][0]);
+                    d[r][1] = fmaf(a.y, k4.y, d[r][1]);
+                    d[r][2] = fmaf(a.z, k4.z, d[r][2]);
+                    d[r][3] = fmaf(a.w, k4.w, d[r][3]);
+                }
             }
-            *reinterpret_cast<float4 *>(S + lane * V32_S_STRIDE + 4u * warp) = make_float4(d0, d1, d2, d3);
+            *reinterpret_cast<float4 *>(S + lane * V32_S_STRIDE + 4u * warp) =
+                make_float4((d[0][0] + d[0][1]) + (d[0][2] + d[0][3]), (d[1][0] + d[1][1]) + (d[1][2] + d[1][3]),
+                            (d[2][0] + d[2][1]) + (d[2][2] + d[2][3]), (d[3][0] + d[3][1]) + (d[3][2] + d[3][3]));
         }
         __syncthreads(); // scores complete; every warp is past the P V of the previous tile
 
