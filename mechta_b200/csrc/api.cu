@@ -23,6 +23,9 @@ void set_error(const char *fmt, ...) {
 }
 
 mkv_status prefill_setup_device();
+mkv_status prefill_tc_setup_device();
+mkv_status launch_prefill_f16_tc(Ctx *ctx, Cache *c, int layer, uint32_t first_pos, uint32_t pos0, uint32_t ntok,
+                                 const float *q, float *out);
 mkv_status append_setup_device();
 mkv_status launch_prefill_f16_mma(Ctx *ctx, Cache *c, int layer, uint32_t first_pos, uint32_t pos0, uint32_t ntok,
                                   const float *q, float *out);
@@ -285,6 +288,7 @@ mkv_status mkv_ctx_create(int device, void *stream, mkv_ctx **out) {
     ctx->counter_base.assign(Ctx::SLOT_ITEMS, 0u);
     mkv_status st = verify_setup_device();
     if (st == MKV_OK) st = prefill_setup_device();
+    if (st == MKV_OK) st = prefill_tc_setup_device();
     if (st == MKV_OK) st = append_setup_device();
     if (st != MKV_OK) return st;
     *out = reinterpret_cast<mkv_ctx *>(ctx);
@@ -701,7 +705,12 @@ mkv_status mkv_attn_prefill(mkv_cache *h, int layer, uint32_t first_pos, uint32_
     }
     mkv_status st = use_device(c->ctx);
     if (st != MKV_OK) return st;
-    if (c->fmt == MKV_F16) return launch_prefill_f16_mma(c->ctx, c, layer, first_pos, pos0, ntok, q, out);
+    if (c->fmt == MKV_F16) {
+        // MKV_PREFILL=mma selects the warp-MMA kernel (kept as the measured baseline of the tcgen05 kernel)
+        static const bool use_mma = [] { const char *e = getenv("MKV_PREFILL"); return e && strcmp(e, "mma") == 0; }();
+        return use_mma ? launch_prefill_f16_mma(c->ctx, c, layer, first_pos, pos0, ntok, q, out)
+                       : launch_prefill_f16_tc(c->ctx, c, layer, first_pos, pos0, ntok, q, out);
+    }
     // f32 cache: groups of up to 4 tokens through the f32 verify kernel (the reference's attn_fd4 also reads
     // K/V once per 4 tokens, W/ops.wgsl:694-699), one ragged batch per <= SLOT_ITEMS groups
     uint32_t done = 0;
