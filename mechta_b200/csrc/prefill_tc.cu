@@ -13,26 +13,27 @@
 // tile maximum exceeds it by more than 8 (the reference's lazy maximum, M/dmx.rs:80 and W/fa_mx.wgsl:120: a
 // matrix accumulator cannot be rescaled per row cheaply), writes P as f16 to shared memory; O += P V (4 MMAs
 // 128x256x16, V used N-major straight from its TMA tile). S of tile j+1 is computed while tile j is in softmax.
-// TMEM: O = columns 0..255, S buffers = 256..319 and 320..383. Every wait is bounded; TMEM is freed on every path.
+// TMEM: O = columns 0..255, S buffers = 256..319 and 320..383, Q (f16, the A operand of Q K^T) = 384..511, which
+// leaves shared memory to a 3-deep K/V ring. Every wait is bounded; TMEM is freed on every path.
+#include <stdlib.h>
+
 #include "internal.cuh"
 #include "ptx.cuh"
 
 namespace mkv {
 using namespace ptx;
 
-constexpr int TC_NST = 2;                              // K/V ring depth
+constexpr int TC_NST = 3;                              // K/V ring depth
 constexpr uint32_t TC_TILE = 64;                       // keys per tile (= PF_TILE, the tensor map's box)
 constexpr uint32_t TC_KV_STAGE = 65536;                // K 32 KB + V 32 KB
 constexpr uint32_t TC_SUB = 8192;                      // [64 keys][64 dims] f16
-constexpr uint32_t TC_QSUB = 16384;                    // [128 rows][64 dims] f16
-constexpr uint32_t TC_OFF_Q = TC_NST * TC_KV_STAGE;    // 4 sub-boxes
-constexpr uint32_t TC_OFF_P = TC_OFF_Q + 4 * TC_QSUB;  // [128 rows][64 keys] f16
+constexpr uint32_t TC_OFF_P = TC_NST * TC_KV_STAGE;    // [128 rows][64 keys] f16
 constexpr uint32_t TC_OFF_BAR = TC_OFF_P + 16384;
 // barriers: kv_full[NST], kv_empty[NST], s_full[2], p_full, pv_done
 constexpr uint32_t TC_NBAR = 2 * TC_NST + 4;
 constexpr uint32_t TC_OFF_MISC = TC_OFF_BAR + TC_NBAR * 8; // tmem base, abort flag
 constexpr uint32_t TC_SMEM = TC_OFF_MISC + 16 + 1024;
-constexpr uint32_t TC_COL_O = 0, TC_COL_S = 256, TC_COLS = 512;
+constexpr uint32_t TC_COL_O = 0, TC_COL_S = 256, TC_COL_Q = 384, TC_COLS = 512;
 constexpr long long TC_WAIT_LIMIT = 2000000000ll;
 constexpr float TC_LAZY = 8.0f;
 
@@ -54,7 +55,8 @@ __device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, TcShared 
 __global__ void __launch_bounds__(192, 1)
 prefill_f16_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
                       const float *__restrict__ q, float *__restrict__ out, uint32_t first_pos, uint32_t pos0, uint32_t ntok,
-                      uint32_t row0, uint32_t *__restrict__ status) {
+                      uint32_t row0, uint32_t *__restrict__ status, uint32_t phase) {
+    // phase (measurement only): 0 = everything, 1 = tile loads only, 2 = loads and MMAs without the softmax math
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *smem = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -85,30 +87,35 @@ prefill_f16_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
     }
     if (warp == 1) tmem_alloc(smem_base + TC_OFF_MISC, TC_COLS); // writes sh->tmem_base
 
-    // Q of the group to shared memory as f16 in the K-major, 128-byte-swizzled layout the MMA descriptors expect:
-    // sub-box b = dims 64b..64b+63, row r at r * 128 bytes, 16-byte chunk c at position c ^ (r & 7)
-    for (uint32_t idx = tid; idx < 128u * 32u; idx += 192u) {
-        const uint32_t row = idx >> 5, chunk = idx & 31u; // chunk = 8 dims
-        const uint32_t tok = tok0 + (row & 15u), head = 8u * kvh + (row >> 4);
-        uint4 w = make_uint4(0, 0, 0, 0);
-        if (tok < ntok) {
-            const float *src = q + (size_t)tok * 4096u + (size_t)head * 256u + chunk * 8u;
-            const float4 a = *reinterpret_cast<const float4 *>(src);
-            const float4 b = *reinterpret_cast<const float4 *>(src + 4);
-            __half2 h0 = __floats2half2_rn(a.x, a.y), h1 = __floats2half2_rn(a.z, a.w);
-            __half2 h2 = __floats2half2_rn(b.x, b.y), h3 = __floats2half2_rn(b.z, b.w);
-            w.x = *reinterpret_cast<uint32_t *>(&h0);
-            w.y = *reinterpret_cast<uint32_t *>(&h1);
-            w.z = *reinterpret_cast<uint32_t *>(&h2);
-            w.w = *reinterpret_cast<uint32_t *>(&h3);
-        }
-        *reinterpret_cast<uint4 *>(smem + TC_OFF_Q + (chunk >> 3) * TC_QSUB + swz128(row, chunk & 7u)) = w;
-    }
-    fence_proxy_async(); // the generic-proxy writes of Q are read by the tensor core through the async proxy
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = sh->tmem_base;
+
+    // Q of the group goes to tensor memory as the A operand of S = Q K^T (q_f16 of the reference, W/fa_mx.wgsl:313-319):
+    // the thread that owns a row converts it to f16 and stores it in its lane, two values per 32-bit column.
+    // Q in TMEM instead of shared memory leaves room for a third K/V stage.
+    if (warp >= 2) {
+        const uint32_t row = 32u * (warp & 3u) + lane, lane_addr = (32u * (warp & 3u)) << 16;
+        const uint32_t tok = tok0 + (row & 15u), head = 8u * kvh + (row >> 4);
+        const float *src = q + (size_t)min(tok, ntok - 1u) * 4096u + (size_t)head * 256u;
+#pragma unroll 1
+        for (uint32_t c0 = 0; c0 < 4u; c0++) { // 64 dims = 32 columns per store
+            uint32_t w[32];
+#pragma unroll
+            for (int i = 0; i < 16; i++) {
+                const float4 a = *reinterpret_cast<const float4 *>(src + c0 * 64u + 4 * i);
+                const __half2 h0 = __floats2half2_rn(a.x, a.y), h1 = __floats2half2_rn(a.z, a.w);
+                w[2 * i] = tok < ntok ? *reinterpret_cast<const uint32_t *>(&h0) : 0u;
+                w[2 * i + 1] = tok < ntok ? *reinterpret_cast<const uint32_t *>(&h1) : 0u;
+            }
+            tmem_st32(tmem + lane_addr + TC_COL_Q + 32u * c0, w);
+        }
+        tmem_wait_st();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -134,13 +141,12 @@ prefill_f16_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
                 const uint32_t s = j % TC_NST;
                 if (!tc_wait(bar_kv_full + 8u * s, (j / TC_NST) & 1u, sh, status)) return false;
                 tc_fence_after();
-                const uint32_t kb = smem_base + s * TC_KV_STAGE, qb = smem_base + TC_OFF_Q;
+                const uint32_t kb = smem_base + s * TC_KV_STAGE;
                 const uint32_t d = tmem + TC_COL_S + 64u * (j & 1u);
 #pragma unroll
                 for (uint32_t ks = 0; ks < 16u; ks++) { // 16 dims per MMA; 4 per 64-dim sub-box
-                    const uint64_t a = tc_desc_sw128(qb + (ks >> 2) * TC_QSUB + (ks & 3u) * 32u, 16, 1024);
                     const uint64_t b = tc_desc_sw128(kb + (ks >> 2) * TC_SUB + (ks & 3u) * 32u, 16, 1024);
-                    tc_mma_f16(d, a, b, IDESC_QK, ks > 0 ? 1u : 0u);
+                    if (phase != 1u) tc_mma_f16_ta(d, tmem + TC_COL_Q + 8u * ks, b, IDESC_QK, ks > 0 ? 1u : 0u);
                 }
                 tc_commit(bar_s_full + 8u * (j & 1u));
                 return true;
@@ -156,7 +162,7 @@ prefill_f16_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
                     const uint64_t a = tc_desc_sw128(pb + ks * 32u, 16, 1024);
                     // V tile [64 keys][64 dims] x 4 sub-boxes, N-major: next 64 dims 8192 bytes on, next 8 keys 1024
                     const uint64_t b = tc_desc_sw128(vb + ks * 2048u, TC_SUB, 1024);
-                    tc_mma_f16(tmem + TC_COL_O, a, b, IDESC_PV, (j > 0 || ks > 0) ? 1u : 0u);
+                    if (phase != 1u) tc_mma_f16(tmem + TC_COL_O, a, b, IDESC_PV, (j > 0 || ks > 0) ? 1u : 0u);
                 }
                 tc_commit(bar_kv_empty + 8u * (j % TC_NST)); // K and V of the stage are free
                 tc_commit(bar_pv_done);                      // O holds tiles 0..j; P may be overwritten
@@ -175,44 +181,58 @@ prefill_f16_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
             // the warp takes every wait's outcome together: the TMEM loads below are warp-collective
             if (!(ok = __all_sync(0xffffffffu, tc_wait(bar_s_full + 8u * (j & 1u), (j >> 1) & 1u, sh, status)))) break;
             tc_fence_after();
+            if (phase != 0u) { // measurement: no softmax math, P left as it is
+                if (j > 0 && !(ok = __all_sync(0xffffffffu, tc_wait(bar_pv_done, (j - 1u) & 1u, sh, status)))) break;
+                tc_fence_before();
+                mbar_arrive(bar_p_full);
+                continue;
+            }
             uint32_t sr[2][32];
             tmem_ld32(tmem + lane_addr + TC_COL_S + 64u * (j & 1u), sr[0]);
             tmem_ld32(tmem + lane_addr + TC_COL_S + 64u * (j & 1u) + 32u, sr[1]);
             tmem_wait_ld();
             const uint32_t key_base = (t0 + j) * TC_TILE;
             const bool need_mask = key_base + TC_TILE > full_below || key_base < first_pos;
+            // work in base-2 exponents: exp(s / 16 - m) = 2^(s * C - m2), C = log2(e) / 16, one FFMA + one ex2 per score
+            constexpr float C2 = SCALE * 1.4426950408889634f;
             float mt = NEG_BIG;
+            if (need_mask) { // tiles that touch the causal diagonal or the window start: scale, then mask (W/fa_mx.wgsl:62)
 #pragma unroll
-            for (int h = 0; h < 2; h++)
+                for (int h = 0; h < 2; h++)
 #pragma unroll
-                for (int c = 0; c < 32; c++) {
-                    float v = __uint_as_float(sr[h][c]) * SCALE; // scale, then mask (W/fa_mx.wgsl:62)
-                    if (need_mask) {
+                    for (int c = 0; c < 32; c++) {
                         const uint32_t key = key_base + 32u * h + c;
-                        if (!(key >= first_pos && key < vis)) v = NEG_BIG;
+                        const float v = (key >= first_pos && key < vis) ? __uint_as_float(sr[h][c]) : NEG_BIG;
+                        sr[h][c] = __float_as_uint(v);
+                        mt = fmaxf(mt, v);
                     }
-                    sr[h][c] = __float_as_uint(v);
-                    mt = fmaxf(mt, v);
-                }
-            // lazy reference maximum: move it only for the first valid tile or when the tile exceeds it by > 8
+            } else {
+#pragma unroll
+                for (int h = 0; h < 2; h++)
+#pragma unroll
+                    for (int c = 0; c < 32; c++) mt = fmaxf(mt, __uint_as_float(sr[h][c]));
+            }
+            mt = mt > NEG_TEST ? mt * C2 : NEG_BIG; // the tile maximum as a base-2 exponent
+            // lazy reference maximum: move it only for the first valid tile or when the tile exceeds it by more than 8
+            // (in natural units, as the reference; 8 * log2(e) here)
             float cf = 1.0f;
-            if (m_ref < NEG_TEST || mt > m_ref + TC_LAZY) {
+            if (mt > NEG_TEST && (m_ref < NEG_TEST || mt > m_ref + TC_LAZY * 1.4426950408889634f)) {
                 const float m_new = fmaxf(m_ref, mt);
-                cf = m_ref > NEG_TEST ? __expf(m_ref - m_new) : 1.0f;
+                cf = m_ref > NEG_TEST ? exp2f(m_ref - m_new) : 1.0f;
                 m_ref = m_new;
             }
+            const float neg_m = m_ref > NEG_TEST ? -m_ref : 0.0f; // masked scores stay at -3e38 * C: 2^that = 0
             float sum = 0.0f;
             uint32_t ph[32]; // 64 weights as f16 pairs
 #pragma unroll
             for (int h = 0; h < 2; h++)
 #pragma unroll
                 for (int c = 0; c < 32; c += 2) {
-                    const float v0 = __uint_as_float(sr[h][c]), v1 = __uint_as_float(sr[h][c + 1]);
-                    const float w0 = v0 > NEG_TEST ? __expf(v0 - m_ref) : 0.0f;
-                    const float w1 = v1 > NEG_TEST ? __expf(v1 - m_ref) : 0.0f;
+                    float w0, w1;
+                    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(w0) : "f"(fmaf(__uint_as_float(sr[h][c]), C2, neg_m)));
+                    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(w1) : "f"(fmaf(__uint_as_float(sr[h][c + 1]), C2, neg_m)));
+                    sum += w0 + w1;
                     const __half2 hp = __floats2half2_rn(w0, w1);
-                    const float2 f = __half22float2(hp);
-                    sum += f.x + f.y;
                     ph[16 * h + (c >> 1)] = *reinterpret_cast<const uint32_t *>(&hp);
                 }
             l_run = l_run * cf + sum;
@@ -282,10 +302,11 @@ mkv_status prefill_tc_setup_device() {
 
 mkv_status launch_prefill_f16_tc(Ctx *ctx, Cache *c, int layer, uint32_t first_pos, uint32_t pos0, uint32_t ntok,
                                  const float *q, float *out) {
+    static const uint32_t phase = [] { const char *e = getenv("MKV_PHASE"); return e ? (uint32_t)atoi(e) : 0u; }();
     const dim3 grid((ntok + 15u) / 16u, 2);
     const CUtensorMap &km = c->maps_host[2 * (c->n_layers + layer)], &vm = c->maps_host[2 * (c->n_layers + layer) + 1];
     prefill_f16_tc_kernel<<<grid, 192, TC_SMEM, ctx->stream>>>(km, vm, q, out, first_pos, pos0, ntok, c->shard_first,
-                                                               ctx->dev_status);
+                                                               ctx->dev_status, phase);
     ctx->launches++;
     MKV_CUDA(cudaGetLastError());
     return MKV_OK;
