@@ -296,7 +296,7 @@ def run_decode(args, workload):
             cache = kv.KvCache(ctx, fmt, N_LAYERS, context)
             sharded = None
         else:
-            sharded = ShardedKvCache(ctx, fmt, N_LAYERS, context, group) if world > 1 else None
+            sharded = ShardedKvCache(ctx, fmt, N_LAYERS, context, group, exchange=args.exchange) if world > 1 else None
             cache = sharded.cache if sharded else kv.KvCache(ctx, fmt, N_LAYERS, context)
         first = cache.shard_first
         rows_here = max(0, min(ctx0, first + cache.capacity) - first)
@@ -429,7 +429,9 @@ def run_decode(args, workload):
                 "vs_baseline": None, "dtype": "f16" if fmt == kv.KvFormat.F16 else "f32", "data": "synthetic",
                 "config": {"workload": workload, "layers": N_LAYERS, "context_tokens": ctx0, "verify_tokens": 4,
                            "cache": fmt.name.lower(), "accept": "uniform 0..3, seed 11", "capacity_tokens": context,
-                           "parallelism": "single GPU" if world == 1 else f"sequence-sharded x{world}, NCCL all-gather of records",
+                           "parallelism": "single GPU" if world == 1 else (
+                               f"sequence-sharded x{world}, records pushed peer to peer over NVLink by the attention kernel"
+                               if args.exchange == "p2p" else f"sequence-sharded x{world}, NCCL all-gather of records"),
                            "l2": "inputs larger than L2: every layer's K+V exceeds 126 MB and 9 other layers are read between reuses",
                            "hbm_frac_of_8TBps_nominal": value / 8000.0 / world},
                 "attn_core_us_per_layer": core_us_max,
@@ -475,6 +477,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, choices=[None, "decode65k", "longctx", "prefill", "sessions"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"], help="how shard records travel between ranks")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

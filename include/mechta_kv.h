@@ -141,6 +141,22 @@ mkv_status mkv_attn_verify_partial(mkv_cache *c, int layer, uint32_t first_pos, 
 mkv_status mkv_combine_shards(mkv_ctx *ctx, const float *recs_dev /*[n_shards][64][258]*/, int n_shards,
                               uint32_t ntok, float *out_dev /*[ntok][16][256]*/);
 
+/* The same exchange without a collective library: each rank's attention kernel stores its record straight into
+ * every rank's mailbox over NVLink (plain peer stores, no multicast) and raises a flag; the merge kernel of each rank
+ * waits (bounded) for the flags of all ranks. One process per GPU; the mailboxes are shared by CUDA IPC:
+ *   mkv_exchange_create on every rank -> mkv_exchange_handle (64 bytes) -> the host gathers the handles of all ranks
+ *   in rank order -> mkv_exchange_connect(handles[world][64]).
+ * Every rank then makes the same sequence of mkv_attn_verify_exchange calls (same layer, positions and q): the call
+ * number is the epoch that flags carry. out_dev = f32 [ntok][16][256], final (merged over all shards) on every rank.
+ * No counterpart in the reference (one GPU); the arithmetic is attn_fd_combine's (W/ops.wgsl:529-537). */
+typedef struct mkv_exchange mkv_exchange;
+mkv_status mkv_exchange_create(mkv_ctx *ctx, int rank, int world, mkv_exchange **out);
+mkv_status mkv_exchange_handle(mkv_exchange *ex, void *handle_out_64_bytes);
+mkv_status mkv_exchange_connect(mkv_exchange *ex, const void *handles /*[world][64] bytes, rank order*/);
+void mkv_exchange_destroy(mkv_exchange *ex);
+mkv_status mkv_attn_verify_exchange(mkv_cache *c, mkv_exchange *ex, int layer, uint32_t first_pos, uint32_t pos,
+                                    uint32_t ntok, const float *q_dev, float *out_dev);
+
 /* Verify attention without any allocation by the library. No counterpart in the reference (which allocates
  * all its buffers once at start-up, M/engine.rs:204-252): this is for hosts that cannot let a library call
  * cudaMalloc — all device memory already belongs to their own planner, or the call comes from a place where

@@ -68,6 +68,12 @@ _SIGS = {
     "mkv_attn_verify_partial": (C.c_int, [C.c_void_p, C.c_int, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p]),
     "mkv_attn_verify_static": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32,
                                          C.c_uint32, C.c_void_p, C.c_void_p]),
+    "mkv_exchange_create": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_void_p)]),
+    "mkv_exchange_handle": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "mkv_exchange_connect": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "mkv_exchange_destroy": (None, [C.c_void_p]),
+    "mkv_attn_verify_exchange": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p,
+                                           C.c_void_p]),
     "mkv_combine_shards": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_uint32, C.c_void_p]),
     "mkv_attn_verify_batch": (C.c_int, [C.c_void_p, C.POINTER(VerifyItem), C.c_int]),
     "mkv_attn_prefill": (C.c_int, [C.c_void_p, C.c_int, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p]),

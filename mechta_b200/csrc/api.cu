@@ -639,6 +639,121 @@ mkv_status mkv_combine_shards(mkv_ctx *h, const float *recs, int n_shards, uint3
     return launch_combine_shards(ctx, recs, n_shards, ntok, out);
 }
 
+// ---- peer exchange of shard records (one process per GPU, CUDA IPC) ----------------------------------------------
+
+mkv_status mkv_exchange_create(mkv_ctx *h, int rank, int world, mkv_exchange **out) {
+    Ctx *ctx = reinterpret_cast<Ctx *>(h);
+    if (!ctx || !out || world < 1 || world > MAX_PEERS || rank < 0 || rank >= world) {
+        set_error("mkv_exchange_create: 1 <= world <= %d and 0 <= rank < world", MAX_PEERS);
+        return MKV_ERR_INVALID;
+    }
+    *out = nullptr;
+    mkv_status st = use_device(ctx);
+    if (st != MKV_OK) return st;
+    Exchange *ex = new (std::nothrow) Exchange();
+    if (!ex) return MKV_ERR_NOMEM;
+    ex->ctx = ctx;
+    ex->rank = rank;
+    ex->world = world;
+    ex->flag_off = (2u * (size_t)world * SLOT_FLOATS * sizeof(float) + 255u) & ~(size_t)255u;
+    ex->mailbox_bytes = ex->flag_off + 256;
+    if (cudaMalloc(&ex->mailbox, ex->mailbox_bytes) != cudaSuccess || cudaMalloc(&ex->push_dev, sizeof(PushInfo)) != cudaSuccess) {
+        cudaGetLastError();
+        set_error("out of device memory for the exchange mailbox");
+        delete ex;
+        return MKV_ERR_NOMEM;
+    }
+    MKV_CUDA(cudaMemset(ex->mailbox, 0, ex->mailbox_bytes));
+    *out = reinterpret_cast<mkv_exchange *>(ex);
+    return MKV_OK;
+}
+
+mkv_status mkv_exchange_handle(mkv_exchange *h, void *handle_out) {
+    Exchange *ex = reinterpret_cast<Exchange *>(h);
+    if (!ex || !handle_out) return MKV_ERR_INVALID;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    mkv_status st = use_device(ex->ctx);
+    if (st != MKV_OK) return st;
+    cudaIpcMemHandle_t hd;
+    MKV_CUDA(cudaIpcGetMemHandle(&hd, ex->mailbox));
+    memcpy(handle_out, &hd, sizeof hd);
+    return MKV_OK;
+}
+
+mkv_status mkv_exchange_connect(mkv_exchange *h, const void *handles) {
+    Exchange *ex = reinterpret_cast<Exchange *>(h);
+    if (!ex || !handles || ex->connected) {
+        set_error("mkv_exchange_connect: null argument or already connected");
+        return MKV_ERR_INVALID;
+    }
+    mkv_status st = use_device(ex->ctx);
+    if (st != MKV_OK) return st;
+    for (int d = 0; d < ex->world; d++) {
+        if (d == ex->rank) {
+            ex->peer_base[d] = ex->mailbox;
+            continue;
+        }
+        cudaIpcMemHandle_t hd;
+        memcpy(&hd, static_cast<const char *>(handles) + 64 * (size_t)d, sizeof hd);
+        MKV_CUDA(cudaIpcOpenMemHandle(&ex->peer_base[d], hd, cudaIpcMemLazyEnablePeerAccess));
+    }
+    PushInfo pi;
+    memset(&pi, 0, sizeof pi);
+    pi.world = (uint32_t)ex->world;
+    pi.rows_done = reinterpret_cast<uint32_t *>(ex->mailbox + ex->flag_off + 2 * MAX_PEERS * sizeof(uint32_t));
+    for (int p = 0; p < 2; p++)
+        for (int d = 0; d < ex->world; d++) {
+            unsigned char *base = static_cast<unsigned char *>(ex->peer_base[d]);
+            pi.slot[p][d] = reinterpret_cast<float *>(base) + ((size_t)p * ex->world + ex->rank) * SLOT_FLOATS;
+            pi.flag[p][d] = reinterpret_cast<uint32_t *>(base + ex->flag_off) + p * MAX_PEERS + ex->rank;
+        }
+    MKV_CUDA(cudaMemcpy(ex->push_dev, &pi, sizeof pi, cudaMemcpyHostToDevice));
+    ex->connected = true;
+    return MKV_OK;
+}
+
+void mkv_exchange_destroy(mkv_exchange *h) {
+    Exchange *ex = reinterpret_cast<Exchange *>(h);
+    if (!ex) return;
+    cudaSetDevice(ex->ctx->device);
+    cudaStreamSynchronize(ex->ctx->stream);
+    for (int d = 0; d < ex->world; d++)
+        if (ex->connected && d != ex->rank && ex->peer_base[d]) cudaIpcCloseMemHandle(ex->peer_base[d]);
+    if (ex->mailbox) cudaFree(ex->mailbox);
+    if (ex->push_dev) cudaFree(ex->push_dev);
+    delete ex;
+}
+
+mkv_status mkv_attn_verify_exchange(mkv_cache *hc, mkv_exchange *hx, int layer, uint32_t first_pos, uint32_t pos, uint32_t ntok,
+                                    const float *q, float *out) {
+    Cache *c = reinterpret_cast<Cache *>(hc);
+    Exchange *ex = reinterpret_cast<Exchange *>(hx);
+    if (!c || !ex || !ex->connected || ex->ctx != c->ctx) {
+        set_error("mkv_attn_verify_exchange: cache and connected exchange of one context needed");
+        return MKV_ERR_INVALID;
+    }
+    VerifyItem it;
+    // the record's destination is the mailboxes; `out` only has to pass the pointer checks here
+    mkv_status st = fill_item(c, layer, first_pos, pos, ntok, q, out, true, &it);
+    if (st != MKV_OK) return st;
+    if ((st = use_device(c->ctx)) != MKV_OK) return st;
+    plan_items(c->ctx, &it, 1);
+    Cache *cc[1] = {c};
+    if ((st = place_scratch(cc, &it, 1)) != MKV_OK) return st;
+    const uint32_t epoch = ++ex->epoch; // every rank makes the same calls, so the call number agrees everywhere
+    it.push = ex->push_dev;
+    it.push_world = (uint32_t)ex->world;
+    it.push_epoch = epoch;
+    it.push_base = ex->rows_base;
+    const uint32_t total = 2u * it.nsplit;
+    if ((st = launch_verify(c->ctx, c->fmt, &it, 1, false, &c->maps_host[2 * layer], &c->maps_host[2 * layer + 1])) != MKV_OK)
+        return st;
+    ex->rows_base += total < 64u ? total : 64u;
+    const float *slots = reinterpret_cast<const float *>(ex->mailbox) + (size_t)(epoch & 1u) * ex->world * SLOT_FLOATS;
+    const uint32_t *flags = reinterpret_cast<const uint32_t *>(ex->mailbox + ex->flag_off) + (epoch & 1u) * MAX_PEERS;
+    return launch_combine_exchange(c->ctx, slots, flags, epoch, ex->world, ntok, out);
+}
+
 mkv_status mkv_attn_verify_batch(mkv_ctx *h, const mkv_verify_item *items, int n) {
     Ctx *ctx = reinterpret_cast<Ctx *>(h);
     if (!ctx || !items || n < 1 || n > Ctx::SLOT_ITEMS) {

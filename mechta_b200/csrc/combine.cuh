@@ -29,9 +29,13 @@ __device__ __forceinline__ void merge_row(const VerifyItem &it, uint32_t r, Fini
     constexpr int NW = NT / 32;
     const uint32_t kvh = r >> 5, row = r & 31u, tok = row >> 3, head = 8u * kvh + (row & 7u);
     const uint32_t tid = threadIdx.x;
+    const uint32_t ndst = it.push ? it.push->world : 1u; // records go to `out`, or to every rank's mailbox
     if (tok >= it.ntok) {
         if (it.partial && tid < 258u) // rows of tokens beyond the step: the empty record
-            it.out[(size_t)(tok * 16u + head) * REC + tid] = tid == 0 ? NEG_BIG : 0.0f;
+            for (uint32_t dd = 0; dd < ndst; dd++) {
+                float *base = it.push ? it.push->slot[it.push_epoch & 1u][dd] : it.out;
+                base[(size_t)(tok * 16u + head) * REC + tid] = tid == 0 ? NEG_BIG : 0.0f;
+            }
         return;
     }
     const uint32_t ns = it.nsplit;
@@ -108,10 +112,13 @@ __device__ __forceinline__ void merge_row(const VerifyItem &it, uint32_t r, Fini
         }
         const float tot = sm.tot;
         if (it.partial) {
-            float *rec = it.out + (size_t)(tok * 16u + head) * REC; // records are 8-byte aligned only
-            *reinterpret_cast<float2 *>(rec + 2 + 4 * tid) = make_float2(a.x, a.y);
-            *reinterpret_cast<float2 *>(rec + 4 + 4 * tid) = make_float2(a.z, a.w);
-            if (tid == 0) *reinterpret_cast<float2 *>(rec) = make_float2(M, tot);
+            for (uint32_t dd = 0; dd < ndst; dd++) { // plain peer stores over NVLink when pushing (no multicast)
+                float *base = it.push ? it.push->slot[it.push_epoch & 1u][dd] : it.out;
+                float *rec = base + (size_t)(tok * 16u + head) * REC; // records are 8-byte aligned only
+                *reinterpret_cast<float2 *>(rec + 2 + 4 * tid) = make_float2(a.x, a.y);
+                *reinterpret_cast<float2 *>(rec + 4 + 4 * tid) = make_float2(a.z, a.w);
+                if (tid == 0) *reinterpret_cast<float2 *>(rec) = make_float2(M, tot);
+            }
         } else {
             const float inv = 1.0f / tot;
             *reinterpret_cast<float4 *>(it.out + (size_t)tok * 4096u + (size_t)head * 256u + 4 * tid) =
@@ -148,6 +155,19 @@ __device__ __forceinline__ void finish_item(const VerifyItem &it, FinishSmem &sm
     __syncthreads();
     if (!sm.ok) return;
     for (uint32_t r = ticket - (total - R); r < 64u; r += R) merge_row<NT>(it, r, sm);
+    if (it.push != nullptr) {
+        // this CTA's rows are on their way to every rank; the last of the R merging CTAs raises the flags
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const uint32_t done = atomicAdd(it.push->rows_done, 1u) - it.push_base;
+            if (done == R - 1u) {
+                __threadfence_system();
+                for (uint32_t dd = 0; dd < it.push->world; dd++)
+                    ptx::st_release_sys(it.push->flag[it.push_epoch & 1u][dd], it.push_epoch);
+            }
+        }
+    }
 }
 
 } // namespace mkv

@@ -35,6 +35,16 @@ void set_error(const char *fmt, ...);
         }                                                                                      \
     } while (0)
 
+// Peer exchange of shard records without a collective library: where a rank's merged record goes.
+constexpr int MAX_PEERS = 8;
+constexpr size_t SLOT_FLOATS = 64 * 258; // one record [64 rows][258]
+struct PushInfo {
+    float *slot[2][MAX_PEERS];    // [epoch parity][destination rank]: this rank's slot in that rank's mailbox
+    uint32_t *flag[2][MAX_PEERS]; // the word that tells the destination the slot is complete (holds the epoch)
+    uint32_t *rows_done;          // local counter of CTAs that finished pushing, never reset
+    uint32_t world;
+};
+
 // One split-K work item of the verify attention: everything a CTA needs, in device memory or in the
 // kernel's parameter space.
 struct VerifyItem {
@@ -57,6 +67,9 @@ struct VerifyItem {
     uint32_t partial;   // 1: write the un-normalised record instead of the final output
     uint32_t *counter;  // arrival counter of this item's CTAs (global memory), never reset
     uint32_t ticket_base; // value of the counter before this launch
+    const PushInfo *push; // partial mode only: push the record to every rank's mailbox instead of `out`
+    uint32_t push_world;  // number of ranks (host copy of push->world)
+    uint32_t push_epoch, push_base; // the exchange's call number; value of rows_done before this launch
     uint32_t safe_below; // keys below this were not written by the kernel launched just before this one
     uint32_t phase;     // measurement only, as the reference's p.f1 phases: 0 = everything, 1 = tile loads only
 };
@@ -125,6 +138,17 @@ struct Cache {
     bool snapshot_pending = false;
 };
 
+struct Exchange {
+    Ctx *ctx = nullptr;
+    int rank = 0, world = 1;
+    unsigned char *mailbox = nullptr; // slots[2][world][SLOT_FLOATS] f32, then flags[2][MAX_PEERS] u32, then rows_done
+    size_t flag_off = 0, mailbox_bytes = 0;
+    void *peer_base[MAX_PEERS] = {};
+    PushInfo *push_dev = nullptr;
+    uint32_t epoch = 0, rows_base = 0;
+    bool connected = false;
+};
+
 // ---- launchers (defined in the .cu files) ---------------------------------------------------------------
 mkv_status launch_append(Ctx *ctx, mkv_fmt fmt, void *const *kbufs, void *const *vbufs, int n_layers,
                          size_t layer_stride_in, uint32_t row_first, uint32_t capacity, uint32_t pos, uint32_t ntok,
@@ -134,6 +158,9 @@ mkv_status launch_verify(Ctx *ctx, mkv_fmt fmt, VerifyItem *items_host, int n, b
                          const CUtensorMap *vmap_host);
 mkv_status verify_setup_device();
 mkv_status launch_combine_shards(Ctx *ctx, const float *recs, int n_shards, uint32_t ntok, float *out);
+mkv_status launch_combine_exchange(Ctx *ctx, const float *slots, const uint32_t *flags, uint32_t epoch, int world, uint32_t ntok,
+                                   float *out);
+mkv_status launch_push_empty(Ctx *ctx, const PushInfo *push, uint32_t epoch, uint32_t world);
 mkv_status launch_prefill(Ctx *ctx, Cache *c, int layer, uint32_t first_pos, uint32_t pos0, uint32_t ntok,
                           const float *q, float *out);
 // plans the split of the items so that the grid fills the SMs once

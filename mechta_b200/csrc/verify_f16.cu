@@ -414,6 +414,67 @@ combine_shards_kernel(const float *__restrict__ recs, int n_shards, float *__res
     out[(size_t)r * 256u + d] = acc / tot;
 }
 
+// The same merge fed by the peer exchange: slots = this rank's mailbox for the call's parity, [world][64][258],
+// written by the other ranks' attention kernels over NVLink; flags[r] holds the call number once rank r's record is
+// complete. The wait is bounded (a rank that never delivers sets the status word, the output is then left alone).
+__global__ void __launch_bounds__(256)
+combine_exchange_kernel(const float *__restrict__ slots, const uint32_t *__restrict__ flags, uint32_t epoch, int world,
+                        float *__restrict__ out, uint32_t *__restrict__ status) {
+    __shared__ uint32_t ok_s;
+    const uint32_t r = blockIdx.x, d = threadIdx.x;
+    if (d == 0) {
+        const long long t0 = clock64();
+        uint32_t ok = 1;
+        for (int g = 0; g < world && ok; g++)
+            while (ld_acquire_sys(flags + g) != epoch) {
+                __nanosleep(64);
+                if (clock64() - t0 > 4000000000ll) {
+                    ok = 0;
+                    atomicOr(status, DEV_ERR_WAIT_TIMEOUT);
+                    break;
+                }
+            }
+        ok_s = ok;
+    }
+    __syncthreads();
+    if (!ok_s) return;
+    float M = NEG_BIG;
+    for (int g = 0; g < world; g++) M = fmaxf(M, __ldcv(slots + ((size_t)g * 64u + r) * REC));
+    float tot = 0.0f, acc = 0.0f;
+    for (int g = 0; g < world; g++) {
+        const float *x = slots + ((size_t)g * 64u + r) * REC;
+        const float e = expf(__ldcv(x) - M);
+        tot += e * __ldcv(x + 1);
+        acc += e * __ldcv(x + 2 + d);
+    }
+    out[(size_t)r * 256u + d] = acc / tot;
+}
+
+// A rank whose shard holds no visible key still owes every rank its (empty) record and flag.
+__global__ void __launch_bounds__(256) push_empty_kernel(const PushInfo *__restrict__ push, uint32_t epoch) {
+    const uint32_t dd = blockIdx.x, tid = threadIdx.x;
+    float *slot = push->slot[epoch & 1u][dd];
+    for (uint32_t i = tid; i < 64u * REC; i += 256u) slot[i] = (i % REC) == 0 ? NEG_BIG : 0.0f;
+    __threadfence_system();
+    __syncthreads();
+    if (tid == 0) st_release_sys(push->flag[epoch & 1u][dd], epoch);
+}
+
+mkv_status launch_combine_exchange(Ctx *ctx, const float *slots, const uint32_t *flags, uint32_t epoch, int world, uint32_t ntok,
+                                   float *out) {
+    combine_exchange_kernel<<<16u * ntok, 256, 0, ctx->stream>>>(slots, flags, epoch, world, out, ctx->dev_status);
+    ctx->launches++;
+    MKV_CUDA(cudaGetLastError());
+    return MKV_OK;
+}
+
+mkv_status launch_push_empty(Ctx *ctx, const PushInfo *push, uint32_t epoch, uint32_t world) {
+    push_empty_kernel<<<world, 256, 0, ctx->stream>>>(push, epoch);
+    ctx->launches++;
+    MKV_CUDA(cudaGetLastError());
+    return MKV_OK;
+}
+
 mkv_status launch_combine_shards(Ctx *ctx, const float *recs, int n_shards, uint32_t ntok, float *out) {
     combine_shards_kernel<<<16u * ntok, 256, 0, ctx->stream>>>(recs, n_shards, out);
     ctx->launches++;
@@ -507,7 +568,10 @@ mkv_status launch_verify(Ctx *ctx, mkv_fmt fmt, VerifyItem *items_host, int n, b
         for (int i = 0; i < n; i++) ctx->counter_base[i] += 2u * items_host[i].nsplit;
     }
     if (ctx->prof) MKV_CUDA(cudaEventRecord(e1, ctx->stream));
-    if (any_empty) {
+    if (any_empty && !batch && items_host[0].push != nullptr) {
+        mkv_status st = launch_push_empty(ctx, items_host[0].push, items_host[0].push_epoch, items_host[0].push_world);
+        if (st != MKV_OK) return st;
+    } else if (any_empty) {
         combine_kernel<<<dim3(64, (unsigned)n), CMB_THREADS, 0, ctx->stream>>>(items_dev, single.item, 1);
         ctx->launches++;
         MKV_CUDA(cudaGetLastError());

@@ -235,6 +235,37 @@ class KvCache:
             pass
 
 
+class KvExchange:
+    """Mailboxes for the peer exchange of shard records (mkv_exchange): every rank's attention kernel stores its
+    record into every rank's mailbox over NVLink, no collective call. `gather_handles(my_handle) -> [bytes] * world`
+    is how the 64-byte IPC handles travel between the processes (e.g. torch.distributed.all_gather_object)."""
+
+    def __init__(self, ctx: KvContext, rank: int, world: int, gather_handles=None):
+        self.ctx, self.rank, self.world = ctx, rank, world
+        self._h = C.c_void_p()
+        check(_lib.lib().mkv_exchange_create(ctx._h, rank, world, C.byref(self._h)))
+        mine = C.create_string_buffer(64)
+        check(_lib.lib().mkv_exchange_handle(self._h, mine))
+        handles = [mine.raw] if world == 1 else gather_handles(mine.raw)
+        assert len(handles) == world and all(len(h) == 64 for h in handles)
+        check(_lib.lib().mkv_exchange_connect(self._h, b"".join(handles)))
+
+    def attn_verify(self, cache: "KvCache", layer: int, first_pos: int, pos: int, q: torch.Tensor, out: torch.Tensor) -> None:
+        """Local record -> peer stores into all mailboxes -> merge; `out` is final on every rank."""
+        check(_lib.lib().mkv_attn_verify_exchange(cache._h, self._h, layer, first_pos, pos, q.shape[0], _ptr(q), _ptr(out)))
+
+    def close(self) -> None:
+        if self._h:
+            _lib.lib().mkv_exchange_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 def write_root_file(path: str, tokens, root: Root) -> None:
     """session.rs:92-111 (KV section; n_ssm = 0)."""
     t = np.ascontiguousarray(tokens, np.uint32)

@@ -51,7 +51,9 @@ class ShardedKvCache:
     from the token's hidden state, which every rank holds).
     """
 
-    def __init__(self, ctx: kv.KvContext, fmt: kv.KvFormat, n_layers: int, context: int, group=None):
+    def __init__(self, ctx: kv.KvContext, fmt: kv.KvFormat, n_layers: int, context: int, group=None, exchange: str = "p2p"):
+        """exchange = "p2p": the attention kernel pushes its record into every rank's mailbox (CUDA IPC, NVLink
+        stores); "nccl": all-gather of the records through torch.distributed, then the merge kernel."""
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
@@ -63,6 +65,13 @@ class ShardedKvCache:
         dev = f"cuda:{ctx.device}"
         self.recs = torch.empty(self.world, 64, 258, device=dev)  # gathered records, one per rank
         self.rec = torch.empty(64, 258, device=dev)
+        self.exchange = None
+        if exchange == "p2p" and self.world > 1:
+            def gather(mine: bytes):
+                got = [None] * self.world
+                dist.all_gather_object(got, mine, group=group)
+                return got
+            self.exchange = kv.KvExchange(ctx, self.rank, self.world, gather)
 
     def owner_of(self, pos: int) -> int:
         return self.plan.owner_of(pos)
@@ -82,11 +91,16 @@ class ShardedKvCache:
         if self.world == 1:
             self.cache.attn_verify(layer, first_pos, pos, q, out)
             return
+        if self.exchange is not None:
+            self.exchange.attn_verify(self.cache, layer, first_pos, pos, q, out)
+            return
         self.cache.attn_verify_partial(layer, first_pos, pos, q, self.rec)
         gather_records(self.rec, self.recs, self.group)
         self.ctx.combine_shards(self.recs, q.shape[0], out)
 
     def close(self):
+        if self.exchange is not None:
+            self.exchange.close()
         self.cache.close()
 
 

@@ -507,3 +507,73 @@ def test_launch_count_and_profiling(ctx, oracle):
     assert n == 3 and 0.0 < ms < 100.0
     assert ctx.launches - n0 == 3  # one kernel per call: the last CTAs merge the pieces
     cache.close()
+
+
+# ---------------------------------------------------------------- peer exchange ----------------------------------
+
+@pytest.mark.parametrize("fmt", FMTS)
+def test_exchange_with_one_rank_equals_plain_verify(ctx, oracle, fmt):
+    """world = 1: the record goes through the mailbox and the flag, the result must equal mkv_attn_verify."""
+    cache = kv.KvCache(ctx, fmt, 1, 4096)
+    kc, vc = fill_both(oracle, cache, 0, 2004, 140)
+    ex = kv.KvExchange(ctx, 0, 1)
+    for i, (first, pos, ntok) in enumerate([(0, 2000, 4), (50, 1500, 2), (0, 2000, 4)]):
+        q = synth.normal(140, synth.S_Q, i, (ntok, 16, 256))
+        a, b = torch.empty(ntok, 16, 256, device="cuda"), torch.full((ntok, 16, 256), float("nan"), device="cuda")
+        cache.attn_verify(0, first, pos, dev(q), a)
+        ex.attn_verify(cache, 0, first, pos, dev(q), b)
+        ctx.sync()
+        want = oracle.attn_ref_f32(int(fmt), kc, vc, first, pos, q)
+        assert oracle.max_rel(b.cpu().numpy(), want) < TOL[fmt]
+        assert oracle.max_rel(b.cpu().numpy(), a.cpu().numpy()) < TOL[fmt]
+    ex.close()
+    cache.close()
+
+
+def _exchange_rank(rank, world, port, ret):
+    import os
+    import torch.distributed as dist
+    from mechta_b200.sharded import ShardedKvCache
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device(f"cuda:{rank}"))
+    st = torch.cuda.Stream()
+    total, pos = 8192, 8192 - 4
+    with torch.cuda.stream(st):
+        c = kv.KvContext(rank, st)
+        outs = {}
+        for mode in ("p2p", "nccl"):
+            sh = ShardedKvCache(c, kv.KvFormat.F16, 1, total, None, exchange=mode)
+            for p in range(0, total, 2048):
+                k = torch.from_numpy(synth.normal(71, synth.S_K, p, (2048, 2, 256))).cuda()
+                v = torch.from_numpy(synth.normal(71, synth.S_V, p, (2048, 2, 256))).cuda()
+                sh.append(0, p, k, v, torch.from_numpy(kv.rope_table(p, 2048)).cuda())
+            out = torch.empty(4, 16, 256, device="cuda")
+            for rep in range(3):  # several calls: the parity slots and epochs are reused
+                q = torch.from_numpy(synth.normal(71, synth.S_Q, rep, (4, 16, 256))).cuda()
+                sh.attn_verify(0, 0, pos, q, out)
+            torch.cuda.synchronize()
+            outs[mode] = out.cpu().numpy()
+            dist.barrier()
+            sh.close()
+        c.sync()
+    if rank == 0:
+        np.savez(ret, **outs)
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_exchange_two_ranks_matches_nccl_and_oracle(oracle, tmp_path):
+    import os
+    import torch.multiprocessing as mp
+    ret = str(tmp_path / "ex.npz")
+    mp.spawn(_exchange_rank, args=(2, 29600 + os.getpid() % 300, ret), nprocs=2, join=True)
+    got = np.load(ret)
+    total, pos = 8192, 8192 - 4
+    kc, vc = oracle.new_cache(0, total), oracle.new_cache(0, total)
+    for p in range(0, total, 2048):
+        oracle.append(0, kc, vc, p, synth.normal(71, synth.S_K, p, (2048, 2, 256)), synth.normal(71, synth.S_V, p, (2048, 2, 256)),
+                      kv.rope_table(p, 2048))
+    want = oracle.attn_ref_f32(0, kc, vc, 0, pos, synth.normal(71, synth.S_Q, 2, (4, 16, 256)))
+    assert oracle.max_rel(got["p2p"], want) < 2e-3 and oracle.max_rel(got["nccl"], want) < 2e-3
+    assert oracle.max_rel(got["p2p"], got["nccl"]) < 1e-6
