@@ -422,6 +422,10 @@ combine_exchange_kernel(const float *__restrict__ slots, const uint32_t *__restr
                         float *__restrict__ out, uint32_t *__restrict__ status) {
     __shared__ uint32_t ok_s;
     const uint32_t r = blockIdx.x, d = threadIdx.x;
+    // Launched with programmatic serialization and without griddepcontrol.wait: everything this kernel reads
+    // arrives through the mailbox and is announced by the flags, its own rank's record included, so it may
+    // start (and wait on the flags) while the attention kernel before it is still finishing.
+    pdl_launch_dependents();
     if (d == 0) {
         const long long t0 = clock64();
         uint32_t ok = 1;
@@ -462,9 +466,17 @@ __global__ void __launch_bounds__(256) push_empty_kernel(const PushInfo *__restr
 
 mkv_status launch_combine_exchange(Ctx *ctx, const float *slots, const uint32_t *flags, uint32_t epoch, int world, uint32_t ntok,
                                    float *out) {
-    combine_exchange_kernel<<<16u * ntok, 256, 0, ctx->stream>>>(slots, flags, epoch, world, out, ctx->dev_status);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(16u * ntok);
+    cfg.blockDim = dim3(256);
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = ctx->pdl ? 1 : 0;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    MKV_CUDA(cudaLaunchKernelEx(&cfg, combine_exchange_kernel, slots, flags, epoch, world, out, ctx->dev_status));
     ctx->launches++;
-    MKV_CUDA(cudaGetLastError());
     return MKV_OK;
 }
 
