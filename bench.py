@@ -37,8 +37,8 @@ N_LAYERS = 10
 KV_BYTES_F16, KV_BYTES_F32 = 2048, 4096  # K + V bytes per position per layer
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the verify kernel at the decode65k shape, from the
-# ncu capture summarised in profiles/verify_f16_kernel_decode65k.md (None until captured)
-NCU_TRAFFIC_BYTES_DECODE65K = None
+# ncu capture summarised in profiles/verify_f16_kernel_decode65k.md (134.44 MB read + 3.8..6.1 MB written)
+NCU_TRAFFIC_BYTES_DECODE65K = 139_400_000
 
 
 def measured_peaks():
@@ -417,6 +417,32 @@ def run_decode(args, workload):
         achieved = (core_bytes / max(core_n, 1)) / (core_us * 1e-6) / 1e9 if core_n else 0.0
         core_us_max = max_over_ranks(torch, world, core_us)
 
+        # strong-scaling reference measured in the same run: rank 0 alone over the whole context, one layer
+        strong_ref = None
+        if world > 1:
+            if rank == 0:
+                whole = kv.KvCache(ctx, fmt, 1, context)
+                for p in range(0, ctx0, 8192):
+                    n = min(8192, ctx0 - p)
+                    k1, v1 = whole.buffer_tensors(0)
+                    k1[p:p + n].normal_(); v1[p:p + n].normal_()
+                whole.set_len(ctx0 + 4)
+                o1 = torch.empty(4, 16, 256, device=dev)
+                for _ in range(3):
+                    whole.attn_verify(0, 0, ctx0, inp.q[0, 0], o1)
+                g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                reps = 20
+                g0.record(stream)
+                for _ in range(reps):
+                    whole.attn_verify(0, 0, ctx0, inp.q[0, 0], o1)
+                g1.record(stream)
+                torch.cuda.synchronize()
+                us1 = 1e3 * g0.elapsed_time(g1) / reps
+                strong_ref = {"n_gpus": 1, "us_per_layer": us1, "value": (ctx0 + 4) * per_pos / (us1 * 1e-6) / 1e9, "unit": "GB/s",
+                              "note": "the same attention launch over the unsharded context on rank 0, one layer"}
+                whole.close()
+            barrier_sync(torch, world)
+
         cpu = None
         if rank == 0 and world == 1 and not args.no_cpu_baseline:
             cpu = cpu_baseline(workload, int(fmt), ctx0, per_pos)
@@ -440,6 +466,7 @@ def run_decode(args, workload):
                              "frac": achieved / peak, "launches_timed": core_n,
                              "traffic": NCU_TRAFFIC_BYTES_DECODE65K if workload == "decode65k" else None},
                 "cpu_baseline": cpu,
+                "strong_ref": strong_ref,
                 "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                         "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
                 "gpu_launches": launches,

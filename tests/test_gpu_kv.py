@@ -261,7 +261,7 @@ def test_steady_state_steps_with_random_accepts(ctx, oracle, fmt):
     cache.close()
 
 
-@pytest.mark.parametrize("fmt,ctx_len", [(kv.KvFormat.F16, 65536), (kv.KvFormat.F32, 32768)])
+@pytest.mark.parametrize("fmt,ctx_len", [(kv.KvFormat.F16, 65536), (kv.KvFormat.F32, 32768), (kv.KvFormat.F32, 131072)])
 def test_verify_full_size_against_oracle(ctx, oracle, fmt, ctx_len):
     """One layer at the benchmark's context length against the oracle, plus linearity in V."""
     cache = kv.KvCache(ctx, fmt, 1, ctx_len + 1024)
@@ -274,13 +274,17 @@ def test_verify_full_size_against_oracle(ctx, oracle, fmt, ctx_len):
     want = oracle.attn_ref_f32(int(fmt), kc, vc, 0, pos, q)
     err = oracle.max_rel(out.cpu().numpy(), want)
     assert err < TOL[fmt], err
-    # scaling V by 2 (exact in both formats) scales the output by 2 exactly
+    # linearity in V: scaling V by 2 (exact in both formats) scales the output by 2 — bit for bit on the f16
+    # cache; on the f32 cache the low halves of the f16 split can be subnormal, so only to f32 rounding
     _, v = cache.buffer_tensors(0)
     v.mul_(2.0)
     out2 = torch.empty_like(out)
     cache.attn_verify(0, 0, pos, dev(q), out2)
     ctx.sync()
-    assert torch.equal(out2, out * 2.0)
+    if fmt == kv.KvFormat.F16:
+        assert torch.equal(out2, out * 2.0)
+    else:
+        assert oracle.max_rel(out2.cpu().numpy(), (out * 2.0).cpu().numpy()) < 1e-6
     cache.close()
 
 
