@@ -286,7 +286,7 @@ def run_decode(args, workload):
         context = min(context, kv.CTX_MAX)
     else:
         fmt, per_pos = kv.KvFormat.F32, KV_BYTES_F32
-        context = kv.CTX_MAX
+        context = kv.check_ctx(args.context or kv.CTX_MAX)
         ctx0 = context - 4 * (steps + warmup) - 8  # the run ends at the last rows of the 262,144-token context
     accepts = synth.accept_counts(11, steps + warmup)
 
@@ -504,6 +504,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, choices=[None, "decode65k", "longctx", "prefill", "sessions"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--context", type=int, default=0, help="longctx only: context tokens (default 262144); smaller for profiling")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"], help="how shard records travel between ranks")
     args = ap.parse_args()
     if args.warmup < 3:
