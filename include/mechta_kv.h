@@ -148,6 +148,9 @@ mkv_status mkv_combine_shards(mkv_ctx *ctx, const float *recs_dev /*[n_shards][6
  *   in rank order -> mkv_exchange_connect(handles[world][64]).
  * Every rank then makes the same sequence of mkv_attn_verify_exchange calls (same layer, positions and q): the call
  * number is the epoch that flags carry. out_dev = f32 [ntok][16][256], final (merged over all shards) on every rank.
+ * A rank whose handle is all zeroes counts as absent: nothing is sent to it, and since its record never arrives the
+ * merge's bounded wait (about two seconds) runs out; the output is then left untouched and mkv_sync reports
+ * MKV_ERR_CUDA (status word), after which the context is usable again.
  * No counterpart in the reference (one GPU); the arithmetic is attn_fd_combine's (W/ops.wgsl:529-537). */
 typedef struct mkv_exchange mkv_exchange;
 mkv_status mkv_exchange_create(mkv_ctx *ctx, int rank, int world, mkv_exchange **out);

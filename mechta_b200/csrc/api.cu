@@ -695,6 +695,12 @@ mkv_status mkv_exchange_connect(mkv_exchange *h, const void *handles) {
         }
         cudaIpcMemHandle_t hd;
         memcpy(&hd, static_cast<const char *>(handles) + 64 * (size_t)d, sizeof hd);
+        bool absent = true; // an all-zero handle = a rank that never joined: nothing is sent to it, its flag never comes
+        for (size_t i = 0; i < sizeof hd; i++) absent &= reinterpret_cast<const unsigned char *>(&hd)[i] == 0;
+        if (absent) {
+            ex->peer_base[d] = nullptr;
+            continue;
+        }
         MKV_CUDA(cudaIpcOpenMemHandle(&ex->peer_base[d], hd, cudaIpcMemLazyEnablePeerAccess));
     }
     PushInfo pi;
@@ -704,6 +710,7 @@ mkv_status mkv_exchange_connect(mkv_exchange *h, const void *handles) {
     for (int p = 0; p < 2; p++)
         for (int d = 0; d < ex->world; d++) {
             unsigned char *base = static_cast<unsigned char *>(ex->peer_base[d]);
+            if (!base) continue;
             pi.slot[p][d] = reinterpret_cast<float *>(base) + ((size_t)p * ex->world + ex->rank) * SLOT_FLOATS;
             pi.flag[p][d] = reinterpret_cast<uint32_t *>(base + ex->flag_off) + p * MAX_PEERS + ex->rank;
         }

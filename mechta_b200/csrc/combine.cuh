@@ -34,7 +34,7 @@ __device__ __forceinline__ void merge_row(const VerifyItem &it, uint32_t r, Fini
         if (it.partial && tid < 258u) // rows of tokens beyond the step: the empty record
             for (uint32_t dd = 0; dd < ndst; dd++) {
                 float *base = it.push ? it.push->slot[it.push_epoch & 1u][dd] : it.out;
-                base[(size_t)(tok * 16u + head) * REC + tid] = tid == 0 ? NEG_BIG : 0.0f;
+                if (base) base[(size_t)(tok * 16u + head) * REC + tid] = tid == 0 ? NEG_BIG : 0.0f;
             }
         return;
     }
@@ -114,6 +114,7 @@ __device__ __forceinline__ void merge_row(const VerifyItem &it, uint32_t r, Fini
         if (it.partial) {
             for (uint32_t dd = 0; dd < ndst; dd++) { // plain peer stores over NVLink when pushing (no multicast)
                 float *base = it.push ? it.push->slot[it.push_epoch & 1u][dd] : it.out;
+                if (!base) continue; // a rank that never joined the exchange
                 float *rec = base + (size_t)(tok * 16u + head) * REC; // records are 8-byte aligned only
                 *reinterpret_cast<float2 *>(rec + 2 + 4 * tid) = make_float2(a.x, a.y);
                 *reinterpret_cast<float2 *>(rec + 4 + 4 * tid) = make_float2(a.z, a.w);
@@ -164,7 +165,7 @@ __device__ __forceinline__ void finish_item(const VerifyItem &it, FinishSmem &sm
             if (done == R - 1u) {
                 __threadfence_system();
                 for (uint32_t dd = 0; dd < it.push->world; dd++)
-                    ptx::st_release_sys(it.push->flag[it.push_epoch & 1u][dd], it.push_epoch);
+                    if (it.push->flag[it.push_epoch & 1u][dd]) ptx::st_release_sys(it.push->flag[it.push_epoch & 1u][dd], it.push_epoch);
             }
         }
     }

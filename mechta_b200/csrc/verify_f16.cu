@@ -458,6 +458,7 @@ combine_exchange_kernel(const float *__restrict__ slots, const uint32_t *__restr
 __global__ void __launch_bounds__(256) push_empty_kernel(const PushInfo *__restrict__ push, uint32_t epoch) {
     const uint32_t dd = blockIdx.x, tid = threadIdx.x;
     float *slot = push->slot[epoch & 1u][dd];
+    if (!slot) return; // a rank that never joined the exchange
     for (uint32_t i = tid; i < 64u * REC; i += 256u) slot[i] = (i % REC) == 0 ? NEG_BIG : 0.0f;
     __threadfence_system();
     __syncthreads();

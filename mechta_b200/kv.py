@@ -247,6 +247,7 @@ class KvExchange:
         mine = C.create_string_buffer(64)
         check(_lib.lib().mkv_exchange_handle(self._h, mine))
         handles = [mine.raw] if world == 1 else gather_handles(mine.raw)
+        handles = [h if h is not None else bytes(64) for h in handles]  # None = a rank that never joined
         assert len(handles) == world and all(len(h) == 64 for h in handles)
         check(_lib.lib().mkv_exchange_connect(self._h, b"".join(handles)))
 

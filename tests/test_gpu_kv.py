@@ -581,3 +581,24 @@ def test_exchange_two_ranks_matches_nccl_and_oracle(oracle, tmp_path):
     want = oracle.attn_ref_f32(0, kc, vc, 0, pos, synth.normal(71, synth.S_Q, 2, (4, 16, 256)))
     assert oracle.max_rel(got["p2p"], want) < 2e-3 and oracle.max_rel(got["nccl"], want) < 2e-3
     assert oracle.max_rel(got["p2p"], got["nccl"]) < 1e-6
+
+
+def test_exchange_with_an_absent_rank_times_out_and_the_context_survives(ctx, oracle):
+    """Failure made on the host: rank 1 of 2 never joins. The merge's bounded wait runs out (about two seconds), the
+    status is reported by sync, nothing hangs, and the context keeps working."""
+    cache = kv.KvCache(ctx, kv.KvFormat.F16, 1, 4096)
+    kc, vc = fill_both(oracle, cache, 0, 1004, 150)
+    ex = kv.KvExchange(ctx, 0, 2, gather_handles=lambda mine: [mine, None])
+    q = synth.normal(150, synth.S_Q, 0, (4, 16, 256))
+    out = torch.full((4, 16, 256), 7.0, device="cuda")
+    ex.attn_verify(cache, 0, 0, 1000, dev(q), out)
+    with pytest.raises(_lib.MkvError) as e:
+        ctx.sync()
+    assert e.value.status == _lib.ERR_CUDA and "wait ran out" in str(e.value)
+    assert bool((out == 7.0).all())  # the merge did not run on incomplete data
+    cache.attn_verify(0, 0, 1000, dev(q), out)  # the context is still usable
+    ctx.sync()
+    want = oracle.attn_ref_f32(0, kc, vc, 0, 1000, q)
+    assert oracle.max_rel(out.cpu().numpy(), want) < 2e-3
+    ex.close()
+    cache.close()
