@@ -161,8 +161,6 @@ static mkv_status fill_item(Cache *c, int layer, uint32_t first_pos, uint32_t po
     memset(it, 0, sizeof *it);
     it->kmap = c->maps_dev + 2 * layer;
     it->vmap = c->maps_dev + 2 * layer + 1;
-    it->kbuf = c->k[layer];
-    it->vbuf = c->v[layer];
     it->q = q;
     it->out = out;
     it->first_pos = first_pos;

@@ -12,6 +12,17 @@
 
 namespace mkv {
 
+// The item a CTA of a verify launch belongs to: the single item in the parameter space, or the staged item
+// whose CTA range contains this CTA.
+__device__ __forceinline__ const VerifyItem &pick_item(const VerifyItem *items, int n_items, const VerifyItem &single,
+                                                       uint32_t cta) {
+    if (items == nullptr) return single;
+    int lo = 0;
+    for (int i = 1; i < n_items; i++)
+        if (cta >= items[i].cta_begin) lo = i;
+    return items[lo];
+}
+
 constexpr int FIN_MAX_THREADS = 512;
 
 struct FinishSmem {
@@ -19,6 +30,9 @@ struct FinishSmem {
     float red[FIN_MAX_THREADS / 32];
     float tot, M;
     uint32_t ticket, ok;
+#ifdef MKV_TRACE
+    unsigned long long tr[3]; // ticket taken, all pieces seen, rows merged
+#endif
     float4 part[FIN_MAX_THREADS / 64][64];
 };
 
@@ -42,10 +56,13 @@ __device__ __forceinline__ void merge_row(const VerifyItem &it, uint32_t r, Fini
     const float2 *ml = reinterpret_cast<const float2 *>(it.part_ml) + (size_t)kvh * ns * 32u + row;
     const uint32_t grp = tid >> 6, d4 = tid & 63u;
     const float4 *po = reinterpret_cast<const float4 *>(it.part_o + ((size_t)kvh * ns * 32u + row) * 256u) + d4;
-    // the first round of piece loads goes out together with the (m, l) loads: neither depends on the other
-    float4 x[5];
+    // The first round of piece loads goes out together with the (m, l) loads: neither depends on the other.
+    // A round is RND loads per thread, all in flight at once: with one CTA per SM on 148 SMs an item has 74
+    // pieces per KV head, which is one round; a second trip to L2 would cost as much as the whole merge.
+    constexpr int RND = 20;
+    float4 x[RND];
 #pragma unroll
-    for (int i = 0; i < 5; i++) {
+    for (int i = 0; i < RND; i++) {
         const uint32_t s = grp + GROUPS * i;
         x[i] = s < ns ? __ldcg(po + (size_t)s * 2048u) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
@@ -83,16 +100,16 @@ __device__ __forceinline__ void merge_row(const VerifyItem &it, uint32_t r, Fini
         if (tid == 0) sm.tot = y;
     }
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (uint32_t s0 = grp; s0 < ns; s0 += GROUPS * 5u) {
-        if (s0 != grp) { // later rounds: five loads issued before any is used
+    for (uint32_t s0 = grp; s0 < ns; s0 += GROUPS * (uint32_t)RND) {
+        if (s0 != grp) { // later rounds
 #pragma unroll
-            for (int i = 0; i < 5; i++) {
+            for (int i = 0; i < RND; i++) {
                 const uint32_t s = s0 + GROUPS * i;
                 x[i] = s < ns ? __ldcg(po + (size_t)s * 2048u) : make_float4(0.f, 0.f, 0.f, 0.f);
             }
         }
 #pragma unroll
-        for (int i = 0; i < 5; i++) {
+        for (int i = 0; i < RND; i++) {
             const uint32_t s = s0 + GROUPS * i;
             const float w = s < ns ? sm.e_s[s] : 0.0f;
             acc.x += w * x[i].x;
@@ -134,7 +151,13 @@ template <int NT>
 __device__ __forceinline__ void finish_item(const VerifyItem &it, FinishSmem &sm, uint32_t *status) {
     const uint32_t total = 2u * it.nsplit;
     __syncthreads(); // every thread's part of the piece precedes thread 0's release below
-    if (threadIdx.x == 0) sm.ticket = ptx::atom_add_release_gpu(it.counter, 1u) - it.ticket_base;
+    if (threadIdx.x == 0) {
+        sm.ticket = ptx::atom_add_release_gpu(it.counter, 1u) - it.ticket_base;
+#ifdef MKV_TRACE
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(sm.tr[0]));
+        sm.tr[1] = sm.tr[2] = 0;
+#endif
+    }
     __syncthreads();
     const uint32_t ticket = sm.ticket;
     const uint32_t R = total < 64u ? total : 64u;
@@ -152,10 +175,17 @@ __device__ __forceinline__ void finish_item(const VerifyItem &it, FinishSmem &sm
         }
         if (!ok) atomicOr(status, DEV_ERR_WAIT_TIMEOUT);
         sm.ok = ok ? 1u : 0u;
+#ifdef MKV_TRACE
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(sm.tr[1]));
+#endif
     }
     __syncthreads();
     if (!sm.ok) return;
     for (uint32_t r = ticket - (total - R); r < 64u; r += R) merge_row<NT>(it, r, sm);
+#ifdef MKV_TRACE
+    __syncthreads();
+    if (threadIdx.x == 0) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(sm.tr[2]));
+#endif
     if (it.push != nullptr) {
         // this CTA's rows are on their way to every rank; the last of the R merging CTAs raises the flags
         __threadfence_system();

@@ -22,7 +22,7 @@ constexpr float SCALE = 1.0f / 16.0f; // M/quad.rs:286 bits(1/16)
 constexpr int MAX_SPLITS = 160;     // upper bound of split-K pieces per KV head of one item
 
 // status word written by kernels instead of trapping (bit set = what went wrong)
-enum : uint32_t { DEV_ERR_WAIT_TIMEOUT = 1u, DEV_ERR_RANGE = 2u };
+enum : uint32_t { DEV_ERR_WAIT_TIMEOUT = 1u };
 
 void set_error(const char *fmt, ...);
 
@@ -50,8 +50,6 @@ struct PushInfo {
 struct VerifyItem {
     const CUtensorMap *kmap; // device address of the layer's K tensor map
     const CUtensorMap *vmap;
-    const void *kbuf; // raw buffers (kernels that do not use TMA)
-    const void *vbuf;
     const float *q; // [ntok][16][256]
     float *out;     // [ntok][16][256], or the [64][258] record in partial mode
     float *part_ml; // [2][nsplit][32][2]
@@ -161,8 +159,6 @@ mkv_status launch_combine_shards(Ctx *ctx, const float *recs, int n_shards, uint
 mkv_status launch_combine_exchange(Ctx *ctx, const float *slots, const uint32_t *flags, uint32_t epoch, int world, uint32_t ntok,
                                    float *out);
 mkv_status launch_push_empty(Ctx *ctx, const PushInfo *push, uint32_t epoch, uint32_t world);
-mkv_status launch_prefill(Ctx *ctx, Cache *c, int layer, uint32_t first_pos, uint32_t pos0, uint32_t ntok,
-                          const float *q, float *out);
 // plans the split of the items so that the grid fills the SMs once
 void plan_items(Ctx *ctx, VerifyItem *items, int n);
 

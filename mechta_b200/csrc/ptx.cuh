@@ -34,6 +34,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// Non-blocking: has the phase with the given parity completed?
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 // Waits for the phase with the given parity, at most ~`limit_cycles` clocks. Returns false on timeout.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, long long limit_cycles) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -54,6 +66,11 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
         "l"(map), "r"(x), "r"(y), "r"(bar)
         : "memory");
 }
+// The same box brought from DRAM into L2 only (no shared-memory destination, no completion to wait for).
+__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap *map, int x, int y) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void prefetch_l2(const void *p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap *map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
@@ -176,10 +193,10 @@ __device__ __forceinline__ uint64_t tc_desc_sw128(uint32_t smem_addr, uint32_t l
     return (uint64_t)((smem_addr >> 4) & 0x3fffu) | ((uint64_t)((lbo_bytes >> 4) & 0x3fffu) << 16) |
            ((uint64_t)((sbo_bytes >> 4) & 0x3fffu) << 32) | (1ull << 46) | (2ull << 61);
 }
-// Instruction descriptor, kind::f16: f16 A and B, f32 D (bit 4), B N-major if `b_mn` (bit 16; A is always
-// K-major here), N / 8 at bits 17-22, M / 16 at bits 24-28.
-__host__ __device__ constexpr uint32_t tc_idesc_f16(uint32_t m, uint32_t n, bool b_mn) {
-    return (1u << 4) | ((b_mn ? 1u : 0u) << 16) | ((n >> 3) << 17) | ((m >> 4) << 24);
+// Instruction descriptor, kind::f16: f16 A and B, f32 D (bit 4), A M-major if `a_mn` (bit 15), B N-major if
+// `b_mn` (bit 16), otherwise K-major; N / 8 at bits 17-22, M / 16 at bits 24-28.
+__host__ __device__ constexpr uint32_t tc_idesc_f16(uint32_t m, uint32_t n, bool b_mn, bool a_mn = false) {
+    return (1u << 4) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
 // byte offset of 16-byte chunk `chunk` of row `row` in a tile whose rows are 128 bytes and which was

@@ -15,6 +15,7 @@
 //  - the CTAs that finish last merge the pieces (combine.cuh), so one launch gives the final output.
 // A variant with two groups of 8 warps taking alternate 32-key tiles was measured slower (76 K against 57 K SM
 // cycles at 65,536 tokens): more barriers per byte and no gain in overlap, since the loop is not compute-bound.
+#include <stdlib.h>
 #include <string.h>
 
 #include "combine.cuh"
@@ -35,15 +36,6 @@ constexpr uint32_t V16_OFF_CF = V16_OFF_P + 32 * 128;
 constexpr uint32_t V16_OFF_BAR = V16_OFF_CF + 32 * 4;
 constexpr uint32_t V16_SMEM = V16_OFF_BAR + V16_NST * 8 + 1024; // + alignment slack
 constexpr long long WAIT_LIMIT = 4000000000ll;   // about two seconds of SM clocks
-
-__device__ __forceinline__ const VerifyItem &pick_item(const VerifyItem *items, int n_items, const VerifyItem &single,
-                                                       uint32_t cta) {
-    if (items == nullptr) return single;
-    int lo = 0;
-    for (int i = 1; i < n_items; i++)
-        if (cta >= items[i].cta_begin) lo = i;
-    return items[lo];
-}
 
 __global__ void __launch_bounds__(256, 1)
 verify_f16_kernel(const VerifyItem *__restrict__ items, int n_items, const __grid_constant__ VerifyLaunch single,
@@ -497,10 +489,23 @@ mkv_status launch_combine_shards(Ctx *ctx, const float *recs, int n_shards, uint
 
 mkv_status launch_verify_f32(Ctx *ctx, const VerifyItem *items_dev, int n, const VerifyLaunch &single, uint32_t total_ctas);
 mkv_status verify_f32_setup_device();
+mkv_status launch_verify_f16_tc(Ctx *ctx, const VerifyItem *items_dev, int n, const VerifyLaunch &single, uint32_t total_ctas);
+mkv_status verify_tc_setup_device();
+
+// MKV_VERIFY=mma selects the warp-MMA kernel of this file for the f16 cache; the default is the tcgen05 kernel.
+static bool verify_use_tc() {
+    static const bool tc = [] {
+        const char *e = getenv("MKV_VERIFY");
+        return !(e && strcmp(e, "mma") == 0);
+    }();
+    return tc;
+}
 
 // dynamic shared memory opt-in for the current device (once per context creation)
 mkv_status verify_setup_device() {
     MKV_CUDA(cudaFuncSetAttribute(verify_f16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)V16_SMEM));
+    mkv_status st = verify_tc_setup_device();
+    if (st != MKV_OK) return st;
     return verify_f32_setup_device();
 }
 
@@ -559,7 +564,10 @@ mkv_status launch_verify(Ctx *ctx, mkv_fmt fmt, VerifyItem *items_host, int n, b
         MKV_CUDA(cudaEventRecord(e0, ctx->stream));
     }
     if (total > 0) {
-        if (fmt == MKV_F16) {
+        if (fmt == MKV_F16 && verify_use_tc()) {
+            mkv_status st = launch_verify_f16_tc(ctx, items_dev, n, single, total);
+            if (st != MKV_OK) return st;
+        } else if (fmt == MKV_F16) {
             // programmatic dependent launch: this kernel's prologue and first tile loads may overlap the tail
             // of the kernel before it in the stream (see pdl_wait in the kernel)
             cudaLaunchConfig_t cfg = {};

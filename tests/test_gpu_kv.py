@@ -288,6 +288,43 @@ def test_verify_full_size_against_oracle(ctx, oracle, fmt, ctx_len):
     cache.close()
 
 
+def test_chained_launches_equal_synchronised_launches(ctx):
+    """The benchmark's launch pattern (several layers at 65,536 tokens, append + verify per step, nothing between the
+    launches) must give bit for bit what the same launches give one at a time: the kernels overlap their neighbours
+    in the stream (early tile loads, L2 prefetch, the merge by the last CTAs), and nothing of that may change a result."""
+    n_layers, n, steps = 4, 65536, 6
+    cache = kv.KvCache(ctx, kv.KvFormat.F16, n_layers, n + 3072)
+    g = torch.Generator(device="cuda"); g.manual_seed(71)
+    for l in range(n_layers):
+        k, v = cache.buffer_tensors(l)
+        k[:n].normal_(generator=g); v[:n].normal_(generator=g)
+    q = torch.randn(steps, n_layers, 4, 16, 256, device="cuda", generator=g)
+    kn = torch.randn(steps, n_layers, 4, 2, 256, device="cuda", generator=g)
+    vn = torch.randn(steps, n_layers, 4, 2, 256, device="cuda", generator=g)
+    acc = synth.accept_counts(72, steps)
+
+    def run(sync_each):
+        cache.set_len(n)
+        pos, outs = n, torch.empty(steps, n_layers, 4, 16, 256, device="cuda")
+        for s in range(steps):
+            cache.append_layers(pos, kn[s], vn[s], dev(kv.rope_table(pos, 4)))
+            for l in range(n_layers):
+                cache.attn_verify(l, 0, pos, q[s, l], outs[s, l])
+                if sync_each:
+                    ctx.sync()
+            pos += 1 + int(acc[s])
+            cache.truncate(pos)
+        ctx.sync()
+        return outs
+
+    a = run(False)
+    b = run(True)
+    c = run(False)
+    assert torch.isfinite(a).all()
+    assert torch.equal(a, b) and torch.equal(a, c)
+    cache.close()
+
+
 # ---------------------------------------------------------------- shards and batches ----------------------------
 
 @pytest.mark.parametrize("fmt", FMTS)
