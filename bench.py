@@ -37,8 +37,8 @@ N_LAYERS = 10
 KV_BYTES_F16, KV_BYTES_F32 = 2048, 4096  # K + V bytes per position per layer
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the verify kernel at the decode65k shape, from the
-# ncu capture summarised in profiles/verify_f16_kernel_decode65k.md (134.44 MB read + 3.8..6.1 MB written)
-NCU_TRAFFIC_BYTES_DECODE65K = 139_400_000
+# ncu capture summarised in profiles/verify_f16_tc_kernel_decode65k.md (139.4..140.2 MB read + 3.1..3.3 MB written)
+NCU_TRAFFIC_BYTES_DECODE65K = 143_000_000
 
 
 def measured_peaks():
@@ -448,7 +448,7 @@ def run_decode(args, workload):
             cpu = cpu_baseline(workload, int(fmt), ctx0, per_pos)
 
         if rank == 0:
-            kernel = "verify_f16_kernel" if fmt == kv.KvFormat.F16 else "verify_f32_kernel"
+            kernel = ("verify_f16_kernel" if os.environ.get("MKV_VERIFY") == "mma" else "verify_f16_tc_kernel") if fmt == kv.KvFormat.F16 else "verify_f32_kernel"
             line = {
                 "metric": "kv_read_gbps", "value": value, "unit": "GB/s", "n_gpus": world, "steps": steps, "warmup": warmup,
                 "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak" if workload == "decode65k" else "strong",

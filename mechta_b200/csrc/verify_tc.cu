@@ -46,7 +46,6 @@ constexpr uint32_t VT_NBAR = 2 * VT_NSLOT + 6;
 constexpr uint32_t VT_OFF_MISC = VT_OFF_BAR + VT_NBAR * 8;
 constexpr uint32_t VT_SMEM = VT_OFF_MISC + 256 + 1024;
 constexpr uint32_t VT_COL_S = 0, VT_COL_O = 64, VT_COLS = 128; // S^T: 2 x 32 columns, O^T: 2 halves x 32
-constexpr int VT_L2_AHEAD = 5;                       // slots asked into L2 while the kernel waits for its predecessor
 constexpr long long VT_WAIT_LIMIT = 2000000000ll;
 constexpr float VT_LOG2E = 1.4426950408889634f;
 constexpr float VT_C2 = SCALE * VT_LOG2E;            // scores to base-2 exponents
@@ -127,13 +126,14 @@ verify_f16_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const uint32_t local = blockIdx.x - it.cta_begin;
     if (local >= 2u * it.nsplit) return;
-    if (it.phase == 2u) return; // measurement: launch cost alone
+    const uint32_t ph = it.phase;
+    if (ph == 2u) return; // measurement: launch cost alone
     pdl_launch_dependents();    // the next kernel in the stream may begin its own prologue
     const uint32_t kvh = local & 1u, split = local >> 1;
     const uint32_t t0 = it.tile_begin + split * it.tiles_per_split; // in 64-key units
     const uint32_t t1 = min(t0 + it.tiles_per_split, it.tile_end);
     const uint32_t k_begin = t0 * TILE, k_end = t1 * TILE;          // this CTA's keys
-    const uint32_t nt = it.phase == 3u ? 0u : (k_end - k_begin + VT_TILE - 1u) / VT_TILE;
+    const uint32_t nt = ph == 3u ? 0u : (k_end - k_begin + VT_TILE - 1u) / VT_TILE;
     const CUtensorMap *kmap = items ? it.kmap : &single.kmap, *vmap = items ? it.vmap : &single.vmap;
     const uint32_t bar0 = smem_base + VT_OFF_BAR;
     const uint32_t bar_full = bar0, bar_empty = bar0 + 8u * VT_NSLOT, bar_s_full = bar0 + 16u * VT_NSLOT;
@@ -168,9 +168,6 @@ verify_f16_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
         mbar_expect_tx(bar, VT_SLOT);
         boxes(n, [&](const CUtensorMap *map, uint32_t off, int x, int y) { tma_load_2d(dst + off, map, x, y, bar); });
     };
-    auto prefetch_item = [&](uint32_t n) { // the same boxes from DRAM into L2 only
-        boxes(n, [&](const CUtensorMap *map, uint32_t, int x, int y) { tma_prefetch_l2_2d(map, x, y); });
-    };
     auto item_safe = [&](uint32_t n) { // does item n lie wholly below safe_below?
         bool is_v;
         return k_begin + (item(n, is_v) + 1u) * VT_TILE <= it.safe_below;
@@ -195,13 +192,11 @@ verify_f16_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
         fence_proxy_async();
         const uint32_t pre = min(2u * nt, (uint32_t)VT_NSLOT);
         for (; early < pre && item_safe(early); early++) issue(early);
-        // Until the kernel before this one has finished, this CTA can use no more than its ring. The tiles after
-        // those are asked into L2 meanwhile, so that DRAM is not idle during the wait and the ring's later loads
-        // hit L2. (A prefetch of rows that are still being written is harmless: L2 is the point of coherence.)
-        const uint32_t pf_end = min(2u * nt, (uint32_t)(VT_NSLOT + VT_L2_AHEAD));
-        for (uint32_t n = VT_NSLOT; n < pf_end; n++) prefetch_item(n);
     }
-    if (tid < 64u * it.ntok) { // Q of this KV head towards L2 as well: 8 KB per token, one 128-byte line per thread
+    // Q of this KV head towards L2 while the kernel waits for its predecessor: 8 KB per token, one 128-byte line
+    // per thread. (Prefetching K/V tiles beyond the ring into L2 in the same way was measured: it takes DRAM
+    // bandwidth from the tail of the kernel in front, which is the critical path, and loses more than it gains.)
+    if (tid < 64u * it.ntok) {
         prefetch_l2(it.q + (size_t)(tid >> 6) * 4096u + (size_t)kvh * 2048u + (size_t)(tid & 63u) * 32u);
     }
     if (warp == 1) tmem_alloc(smem_base + VT_OFF_MISC, VT_COLS); // writes sh->tmem_base
@@ -237,6 +232,7 @@ verify_f16_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = sh->tmem_base;
+    if (tid == 0) { VT_TRACE(5); }
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -249,7 +245,7 @@ verify_f16_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
-        if (lane == 0 && it.phase == 1u) { // measurement: stream the tiles only
+        if (lane == 0 && ph == 1u) { // measurement: stream the tiles only
             for (uint32_t i = 0; i < 2u * nt; i++) {
                 if (!vt_wait(bar_full + 8u * (i % VT_NSLOT), (i / VT_NSLOT) & 1u, sh, status)) break;
                 mbar_arrive(bar_empty + 8u * (i % VT_NSLOT));
@@ -258,7 +254,7 @@ verify_f16_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
             constexpr uint32_t IDESC_QK = tc_idesc_f16(128, 32, false, false);
             constexpr uint32_t IDESC_PV = tc_idesc_f16(128, 32, false, true);
             const uint32_t qb = smem_base + VT_OFF_Q, pb = smem_base + VT_OFF_P;
-            const bool mma_qk = it.phase != 5u, mma_pv = it.phase != 5u; // measurement: 5 = everything but the MMAs
+            const bool mma_qk = ph != 5u, mma_pv = ph != 5u; // measurement: 5 = everything but the MMAs
             // Event loop: whichever of "the next K tile has landed" (and its S^T buffer is free) and "the next V
             // tile has landed and its P^T is written" is true first is issued first, so that a tile's shared
             // memory goes back to the producer as early as possible: the bytes in flight, not the tensor pipe,
@@ -353,13 +349,16 @@ verify_f16_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
         // P^T[row][key]: this thread's column, 2 bytes in each of the 32 rows (K-major B operand, 128-byte swizzle)
         uint8_t *pcol = smem + VT_OFF_P + (klane >> 6) * 4096u + (klane & 7u) * 2u;
         const uint32_t kchunk = (klane & 63u) >> 3;
-        const uint32_t nts = it.phase == 1u ? 0u : nt;
+        const uint32_t nts = ph == 1u ? 0u : nt;
         bool stopped = false;
         for (uint32_t j = 0; j < nts; j++) {
             // a warp takes every wait's outcome together: the TMEM loads are warp-collective
             bool ok = __all_sync(0xffffffffu, vt_wait(bar_s_full + 8u * (j & 1u), (j >> 1) & 1u, sh, status));
             tc_fence_after();
-            if (it.phase == 4u) { // measurement: the MMAs without the softmax math, P^T left as it is
+#ifdef MKV_TRACE
+            if (tid == 128 && j == 0) sh->tq[7] = vt_now();
+#endif
+            if (ph == 4u) { // measurement: the MMAs without the softmax math, P^T left as it is
                 if (j > 1) __all_sync(0xffffffffu, vt_wait(bar_pv_done + 8u * (j & 1u), ((j >> 1) - 1u) & 1u, sh, status));
                 tc_fence_before();
                 mbar_arrive(bar_p_full + 8u * (j & 1u));
@@ -439,6 +438,9 @@ verify_f16_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
                     tmem_wait_st();
                 }
             }
+#ifdef MKV_TRACE
+            if (tid == 128 && j == 0) sh->tp[7] = vt_now();
+#endif
             // weights: 2^(t - m), rounded to f16 as the reference does (M/dmx.rs:99); the sums run over the rounded values
 #pragma unroll
             for (int r = 0; r < 32; r++) {
@@ -522,7 +524,7 @@ verify_f16_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
             r[7] = tr[4]; r[8] = vt_now(); r[9] = reinterpret_cast<FinishSmem *>(smem)->ticket;
             for (int i = 0; i < 3; i++) r[10 + i] = reinterpret_cast<FinishSmem *>(smem)->tr[i];
             for (int i = 0; i < 8; i++) { r[13 + i] = tq8[i]; r[21 + i] = tp8[i]; r[29 + i] = ts8[i]; }
-            r[37] = nt;
+            r[37] = nt; r[38] = tr[5];
         }
     }
 #endif

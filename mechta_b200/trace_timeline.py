@@ -1,0 +1,108 @@
+"""Timeline of the decode attention kernel inside a chain of launches, and the per-launch time of that chain.
+
+    make -C mechta_b200/csrc trace                         # builds mechta_b200/libmechta_kv_trace.so (-DMKV_TRACE)
+    python -m mechta_b200.trace_timeline --context 65536   # timeline + microseconds per launch
+    python -m mechta_b200.trace_timeline --context 262144 --no-trace   # stock library, per-launch time only
+
+The trace build makes every CTA of verify_f16_tc_kernel record %globaltimer at its start, after
+griddepcontrol.wait, at each batch of MMAs, when its piece is written, in the merge and at its exit. The loop is
+the benchmark's: per step one append of 4 rows to all layers, then one verify launch per layer, nothing between
+the launches. Times are medians over the CTAs of one launch, in microseconds from the launch's first CTA start.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import os
+
+import numpy as np
+
+FIELDS = 40  # uint64 per record, see verify_tc.cu
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--context", type=int, default=65536)
+    ap.add_argument("--layers", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=6)
+    ap.add_argument("--no-trace", action="store_true", help="use the stock library: per-launch time only")
+    args = ap.parse_args()
+
+    import torch
+    from mechta_b200 import _lib
+    if not args.no_trace:
+        so = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libmechta_kv_trace.so")
+        if not os.path.exists(so):
+            raise SystemExit("build the trace library first: make -C mechta_b200/csrc trace")
+        _lib.SO_PATH = so
+    from mechta_b200 import kv
+
+    torch.cuda.set_device(0)
+    st = torch.cuda.Stream()
+    n, nl = args.context, args.layers
+    with torch.cuda.stream(st):
+        ctx = kv.KvContext(0, st)
+        lib = _lib.lib()
+        cache = kv.KvCache(ctx, kv.KvFormat.F16, nl, min(kv.CTX_MAX, n + 1024))
+        n = min(n, cache.capacity - 64)
+        for l in range(nl):
+            k, v = cache.buffer_tensors(l)
+            k.normal_(); v.normal_()
+        cache.set_len(n)
+        q = torch.randn(nl, 4, 16, 256, device="cuda")
+        out = torch.empty_like(q)
+        kn = torch.randn(nl, 4, 2, 256, device="cuda")
+        vn = torch.randn(nl, 4, 2, 256, device="cuda")
+        pos = n
+
+        def step(pos):
+            cache.append_layers(pos, kn, vn, torch.from_numpy(kv.rope_table(pos, 4)).cuda())
+            for l in range(nl):
+                cache.attn_verify(l, 0, pos, q[l], out[l])
+            cache.truncate(pos + 2)
+            return pos + 2
+
+        for _ in range(5):
+            pos = step(pos)
+        torch.cuda.synchronize()
+        buf = np.zeros((65536, FIELDS), dtype=np.uint64)
+        if not args.no_trace:
+            lib.mkv_trace_read.restype = C.c_int
+            lib.mkv_trace_read(buf.ctypes.data_as(C.c_void_p), 65536)  # drop the warm-up records
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(st)
+        for _ in range(args.steps):
+            pos = step(pos)
+        e1.record(st)
+        torch.cuda.synchronize()
+        print(f"context {n}: {1e3 * e0.elapsed_time(e1) / (args.steps * nl):.2f} us per launch (append included), "
+              f"{n * 2048 * args.steps * nl / e0.elapsed_time(e1) / 1e6:.0f} GB/s")
+        if args.no_trace:
+            return
+        cnt = lib.mkv_trace_read(buf.ctypes.data_as(C.c_void_p), 65536)
+        r = buf[:cnt].astype(np.int64)
+        launches = sorted(set(r[:, 0].tolist()))
+        prev_t0 = None
+        for la in launches[-4:]:
+            x = r[r[:, 0] == la]
+            t0 = x[:, 3].min()
+            us = lambda col, rows=x: (rows[:, col] - t0) / 1e3
+            period = (t0 - prev_t0) / 1e3 if prev_t0 is not None else float("nan")
+            prev_t0 = t0
+            print(f"launch (ticket base {la}): {len(x)} CTAs, period {period:.2f}")
+            print(f"  start med {np.median(us(3)):.2f} max {us(3).max():.2f} | wait returns med {np.median(us(4)):.2f} | "
+                  f"Q ready med {np.median(us(38)):.2f} | first S^T med {np.median(us(5)):.2f} | "
+                  f"last O^T med {np.median(us(6)):.2f} max {us(6).max():.2f} | last piece {us(7).max():.2f} | "
+                  f"exit med {np.median(us(8)):.2f} max {us(8).max():.2f}")
+            m = x[x[:, 11] > 0]
+            if len(m):
+                print(f"  {len(m)} merging CTAs: ticket med {np.median(us(10, m)):.2f} | all pieces seen med {np.median(us(11, m)):.2f} | "
+                      f"merged max {us(12, m).max():.2f}")
+            nt = int(np.bincount(x[:, 37]).argmax())
+            full = x[x[:, 37] == nt]
+            for name, c0 in (("S^T issued", 13), ("softmax done", 29), ("O^T issued", 21)):
+                print(f"  {name:13s}", " ".join(f"{np.median(us(c0 + j, full)):6.2f}" for j in range(min(nt, 7))))
+
+
+if __name__ == "__main__":
+    main()
