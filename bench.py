@@ -502,7 +502,7 @@ def main():
     ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=None, choices=[None, "decode65k", "longctx", "prefill", "sessions"])
+    ap.add_argument("--workload", default=None, choices=[None, "decode65k", "longctx", "prefill", "sessions", "step65k"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--context", type=int, default=0, help="longctx only: context tokens (default 262144); smaller for profiling")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"], help="how shard records travel between ranks")

@@ -188,6 +188,25 @@ typedef struct {
 } mkv_verify_item;
 mkv_status mkv_attn_verify_batch(mkv_ctx *ctx, const mkv_verify_item *items, int n);
 
+/* The layer's whole step around the KV path in two launches. Replaces, for the ntok rows of a step, the nine
+ * dispatches of engine/crates/mechta/src/quad.rs:113-125: rmsnorm of the query heads and of the key heads
+ * (wgsl/ops.wgsl:27-56 with attn_q_norm / attn_k_norm), rope2 of the queries (ops.wgsl:275-286), kv_rope2 and
+ * kv_copy into the cache (wgsl/kv.wgsl:19-42), q_dmx, attn_dmx2 or attn_fd, attn_fd_combine, and attn_gate /
+ * attn_gate16 (ops.wgsl:171-177, 295-300). Rows [pos, pos + ntok) of the layer are written exactly as mkv_append
+ * would write the normalised keys; the result is the gated attention output. Unsharded caches only. */
+typedef struct {
+    const float *qf_dev;       /* [ntok][16][512]: per head 256 query values, then 256 gate values (output of attn_q) */
+    const float *kb_dev;       /* [ntok][2][256]: output of attn_k, before its norm */
+    const float *vb_dev;       /* [ntok][512]: output of attn_v */
+    const float *q_norm_dev;   /* [256] attn_q_norm.weight */
+    const float *k_norm_dev;   /* [256] attn_k_norm.weight */
+    const float *rope_tab_dev; /* [ntok][64] as mkv_rope_table */
+    float eps;                 /* 1e-6 in the reference (engine.rs:12) */
+} mkv_step_in;
+/* ag_dev: [ntok][16][256] f32 (attn_gate), ag16_dev: the same values as f16 (attn_gate16); either may be NULL. */
+mkv_status mkv_attn_step(mkv_cache *c, int layer, uint32_t first_pos, uint32_t pos, uint32_t ntok, const mkv_step_in *in,
+                         float *ag_dev, void *ag16_dev);
+
 /* ---- prefill attention over the cache: replaces q_f16 + attn_fa_mx + attn_fd_combine (W/fa_mx.wgsl:19-115,
  * 313-319), attn_fa and attn_fd4 (W/ops.wgsl:562-651,711-778), dispatched at M/engine.rs:1215-1241.
  * The block's K/V must already be appended (the reference appends all rows first, M/engine.rs:1213-1214).

@@ -26,6 +26,12 @@ class MkvError(RuntimeError):
         self.status = status
 
 
+class StepIn(C.Structure):
+    """mkv_step_in of include/mechta_kv.h."""
+    _fields_ = [("qf_dev", C.c_void_p), ("kb_dev", C.c_void_p), ("vb_dev", C.c_void_p), ("q_norm_dev", C.c_void_p),
+                ("k_norm_dev", C.c_void_p), ("rope_tab_dev", C.c_void_p), ("eps", C.c_float)]
+
+
 class VerifyItem(C.Structure):
     """mkv_verify_item of include/mechta_kv.h."""
     _fields_ = [("cache", C.c_void_p), ("layer", C.c_int32), ("first_pos", C.c_uint32), ("pos", C.c_uint32),
@@ -76,6 +82,7 @@ _SIGS = {
                                            C.c_void_p]),
     "mkv_combine_shards": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_uint32, C.c_void_p]),
     "mkv_attn_verify_batch": (C.c_int, [C.c_void_p, C.POINTER(VerifyItem), C.c_int]),
+    "mkv_attn_step": (C.c_int, [C.c_void_p, C.c_int, C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(StepIn), C.c_void_p, C.c_void_p]),
     "mkv_attn_prefill": (C.c_int, [C.c_void_p, C.c_int, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p]),
     "mkv_snapshot_bytes": (C.c_size_t, [C.c_void_p, C.c_uint32]),
     "mkv_snapshot": (C.c_int, [C.c_void_p, C.c_uint32, C.c_void_p, C.c_size_t, C.POINTER(C.c_size_t)]),

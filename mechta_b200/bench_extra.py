@@ -3,6 +3,9 @@
 prefill   Prefix-cache restore + prefill: a 32,768-token f16 snapshot of 10 layers is restored from pinned host
           memory, a 2,048-token block is appended and attends to the prefix and to itself (causal), and 34,816 rows are
           snapshotted back. One step = all of that. Reported: attention TFLOP/s against the tensor peak, copy GB/s.
+step65k   decode65k with the layer's whole step around the KV path fused (mkv_attn_step): per layer one launch for
+          rmsnorm of q and k heads + RoPE + the cache rows, one for attention + merge + output gate, i.e. 20 launches
+          per step where the reference's dispatch list has 90.
 sessions  32 concurrent sessions with ragged f16 caches (lengths uniform in [1,024, 131,072]), spread over the ranks
           by KV bytes (greedy, longest first), 10 layers, one 4-token verify per session per step with its own accept
           count. No collective: sessions are independent.
@@ -28,7 +31,72 @@ def _peaks(root):
 def run(args, workload):
     if workload == "prefill":
         return run_prefill(args)
+    if workload == "step65k":
+        return run_step(args)
     return run_sessions(args)
+
+
+def run_step(args):
+    import torch
+    from mechta_b200 import kv, synth
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    torch.cuda.set_device(0)
+    stream = torch.cuda.Stream()
+    steps, warmup, ctx0 = args.steps, args.warmup, 65536
+    with torch.cuda.stream(stream):
+        ctx = kv.KvContext(0, stream)
+        cache = kv.KvCache(ctx, kv.KvFormat.F16, N_LAYERS, (ctx0 + 4 * (steps + warmup) + 8 + 1023) // 1024 * 1024)
+        g = torch.Generator(device="cuda"); g.manual_seed(7)
+        for l in range(N_LAYERS):  # synthetic rows written straight into the buffers
+            k, v = cache.buffer_tensors(l)
+            k[:ctx0].normal_(generator=g); v[:ctx0].normal_(generator=g)
+        cache.set_len(ctx0)
+        ring = 8
+        qf = torch.randn(ring, N_LAYERS, 4, 16, 512, device="cuda", generator=g)
+        kb = torch.randn(ring, N_LAYERS, 4, 2, 256, device="cuda", generator=g)
+        vb = torch.randn(ring, N_LAYERS, 4, 512, device="cuda", generator=g)
+        qw = 1.0 + 0.1 * torch.randn(N_LAYERS, 256, device="cuda", generator=g)
+        kw = 1.0 + 0.1 * torch.randn(N_LAYERS, 256, device="cuda", generator=g)
+        tabs = torch.from_numpy(kv.rope_table(ctx0, 4 * (steps + warmup) + 8)).cuda()
+        out16 = torch.empty(N_LAYERS, 4, 16, 256, device="cuda", dtype=torch.float16)
+        acc = synth.accept_counts(11, steps + warmup)
+
+        def step(s, pos):
+            r = s % ring
+            tab = tabs[pos - ctx0:pos - ctx0 + 4]
+            for l in range(N_LAYERS):
+                cache.attn_step(l, 0, pos, qf[r, l], kb[r, l], vb[r, l], qw[l], kw[l], tab, None, out16[l])
+            new_len = pos + 1 + int(acc[s])
+            cache.truncate(new_len)
+            return new_len
+
+        pos = ctx0
+        for s in range(warmup):
+            pos = step(s, pos)
+        torch.cuda.synchronize()
+        n0 = ctx.launches
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        total = 0
+        e0.record(stream)
+        for s in range(warmup, warmup + steps):
+            total += N_LAYERS * (pos + 4) * 2048
+            pos = step(s, pos)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        hbm, _, kind = _peaks(root)
+        value = total / (ms * 1e-3) / 1e9
+        line = {"metric": "kv_read_gbps", "value": value, "unit": "GB/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+                "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
+                "data": "synthetic",
+                "config": {"workload": "step65k", "layers": N_LAYERS, "context_tokens": ctx0, "verify_tokens": 4, "cache": "f16",
+                           "fused": "rmsnorm(q,k) + rope2 + kv_rope2 + kv_copy | attention + merge + attn_gate16",
+                           "launches_per_step": (ctx.launches - n0) // steps, "reference_dispatches_per_step": 9 * N_LAYERS},
+                "roofline": {"bound": "hbm", "kernel": "verify_f16_tc_kernel", "achieved": value, "peak": hbm, "peak_kind": kind,
+                             "unit": "GB/s", "frac": value / hbm, "traffic": None},
+                "gpu_launches": ctx.launches - n0}
+        print(json.dumps(line), flush=True)
+        cache.close()
 
 
 def run_prefill(args):

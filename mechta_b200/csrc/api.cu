@@ -471,6 +471,11 @@ mkv_status mkv_cache_create(mkv_ctx *h, mkv_fmt fmt, int n_layers, uint32_t cont
         return fail(MKV_ERR_CUDA);
     }
     if ((st = ensure_scratch(c, 2u * (size_t)ctx->sm_count)) != MKV_OK) return fail(st);
+    if (cudaMalloc(&c->qr, (size_t)MKV_MAX_VERIFY * 16 * 256 * sizeof(float)) != cudaSuccess) {
+        cudaGetLastError();
+        set_error("out of device memory for the query scratch");
+        return fail(MKV_ERR_NOMEM);
+    }
     *out = reinterpret_cast<mkv_cache *>(c);
     return MKV_OK;
 }
@@ -490,6 +495,7 @@ void mkv_cache_destroy(mkv_cache *h) {
     if (c->vptrs_dev) cudaFree(c->vptrs_dev);
     if (c->part_ml) cudaFree(c->part_ml);
     if (c->part_o) cudaFree(c->part_o);
+    if (c->qr) cudaFree(c->qr);
     if (c->ev_snapshot) cudaEventDestroy(c->ev_snapshot);
     Ctx *ctx = c->ctx;
     delete c;
@@ -619,6 +625,64 @@ mkv_status mkv_truncate(mkv_cache *h, uint32_t new_len, int scrub) {
 
 mkv_status mkv_attn_verify(mkv_cache *h, int layer, uint32_t first_pos, uint32_t pos, uint32_t ntok, const float *q, float *out) {
     return verify_common(reinterpret_cast<Cache *>(h), layer, first_pos, pos, ntok, q, out, false);
+}
+
+mkv_status mkv_attn_step(mkv_cache *h, int layer, uint32_t first_pos, uint32_t pos, uint32_t ntok, const mkv_step_in *in,
+                         float *ag, void *ag16) {
+    Cache *c = reinterpret_cast<Cache *>(h);
+    if (!c || !in) {
+        set_error("null cache or inputs");
+        return MKV_ERR_INVALID;
+    }
+    if (!in->qf_dev || !in->kb_dev || !in->vb_dev || !in->q_norm_dev || !in->k_norm_dev || !in->rope_tab_dev || (!ag && !ag16)) {
+        set_error("mkv_attn_step needs qf, kb, vb, both norm weights, the rope table and at least one output");
+        return MKV_ERR_INVALID;
+    }
+    if (((uintptr_t)in->qf_dev & 15u) || ((uintptr_t)ag & 15u) || ((uintptr_t)ag16 & 7u)) {
+        set_error("qf and ag must be 16-byte aligned, ag16 8-byte aligned");
+        return MKV_ERR_INVALID;
+    }
+    if (!c->whole) {
+        set_error("mkv_attn_step works on an unsharded cache: the gate follows the merge of all shards");
+        return MKV_ERR_UNSUPPORTED;
+    }
+    if (!(in->eps > 0.0f)) {
+        set_error("eps must be positive");
+        return MKV_ERR_INVALID;
+    }
+    // the same checks as an append of these rows followed by a verify over them
+    VerifyItem it;
+    const uint32_t len_before = c->len, lw_before = c->last_write_pos;
+    const uint64_t end = (uint64_t)pos + ntok;
+    if (layer < 0 || layer >= c->n_layers || ntok < 1 || ntok > MKV_MAX_VERIFY || end > (uint64_t)c->context) {
+        set_error("layer %d, rows [%u, %llu) outside the cache (layers %d, context %u, at most %d rows a step)", layer, pos,
+                  (unsigned long long)end, c->n_layers, c->context, MKV_MAX_VERIFY);
+        return end > (uint64_t)c->context ? MKV_ERR_CAPACITY : MKV_ERR_INVALID;
+    }
+    if (c->len < pos) {
+        set_error("rows up to %u are valid, the step would leave a gap before %u", c->len, pos);
+        return MKV_ERR_STATE;
+    }
+    c->len = (uint32_t)end; // the rows this call writes count as valid for its own attention
+    c->last_write_pos = pos;
+    // fill_item wants an output pointer for its checks; the f16 one serves when there is no f32 output
+    mkv_status st = fill_item(c, layer, first_pos, pos, ntok, c->qr, ag ? ag : static_cast<float *>(ag16), false, &it);
+    if (st == MKV_OK) st = use_device(c->ctx);
+    if (st != MKV_OK) {
+        c->len = len_before;
+        c->last_write_pos = lw_before;
+        return st;
+    }
+    it.out = ag;
+    it.gate = in->qf_dev;
+    it.out16 = ag16;
+    st = launch_step_prep(c->ctx, c->fmt, in->qf_dev, in->kb_dev, in->vb_dev, in->q_norm_dev, in->k_norm_dev, in->rope_tab_dev,
+                          in->eps, c->qr, c->k[layer], c->v[layer], c->shard_first, c->capacity, pos, ntok);
+    if (st != MKV_OK) return st;
+    plan_items(c->ctx, &it, 1);
+    Cache *cc[1] = {c};
+    if ((st = place_scratch(cc, &it, 1)) != MKV_OK) return st;
+    return launch_verify(c->ctx, c->fmt, &it, 1, false, &c->maps_host[2 * layer], &c->maps_host[2 * layer + 1]);
 }
 
 mkv_status mkv_attn_verify_partial(mkv_cache *h, int layer, uint32_t first_pos, uint32_t pos, uint32_t ntok, const float *q,

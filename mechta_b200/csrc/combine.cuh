@@ -139,8 +139,21 @@ __device__ __forceinline__ void merge_row(const VerifyItem &it, uint32_t r, Fini
             }
         } else {
             const float inv = 1.0f / tot;
-            *reinterpret_cast<float4 *>(it.out + (size_t)tok * 4096u + (size_t)head * 256u + 4 * tid) =
-                make_float4(a.x * inv, a.y * inv, a.z * inv, a.w * inv);
+            float4 y = make_float4(a.x * inv, a.y * inv, a.z * inv, a.w * inv);
+            const size_t o = (size_t)tok * 4096u + (size_t)head * 256u + 4 * tid;
+            if (it.gate) { // attn_gate of the reference (W/ops.wgsl:171-177): times the sigmoid of the head's gate values
+                const float4 g = *reinterpret_cast<const float4 *>(it.gate + ((size_t)tok * 16u + head) * 512u + 256u + 4 * tid);
+                y.x *= 1.0f / (1.0f + expf(-g.x));
+                y.y *= 1.0f / (1.0f + expf(-g.y));
+                y.z *= 1.0f / (1.0f + expf(-g.z));
+                y.w *= 1.0f / (1.0f + expf(-g.w));
+            }
+            if (it.out) *reinterpret_cast<float4 *>(it.out + o) = y;
+            if (it.out16) { // attn_gate16 (W/ops.wgsl:295-300): the same values as f16
+                const __half2 h0 = __floats2half2_rn(y.x, y.y), h1 = __floats2half2_rn(y.z, y.w);
+                *reinterpret_cast<uint2 *>(static_cast<__half *>(it.out16) + o) =
+                    make_uint2(*reinterpret_cast<const uint32_t *>(&h0), *reinterpret_cast<const uint32_t *>(&h1));
+            }
         }
     }
 }

@@ -69,6 +69,8 @@ struct VerifyItem {
     uint32_t push_world;  // number of ranks (host copy of push->world)
     uint32_t push_epoch, push_base; // the exchange's call number; value of rows_done before this launch
     uint32_t safe_below; // keys below this were not written by the kernel launched just before this one
+    const float *gate;   // final mode only: [ntok][16][512] with the output gate in the second half of each head, or null
+    void *out16;         // final mode only: the output once more as f16 [ntok][16][256], or null
     uint32_t phase;     // measurement only, as the reference's p.f1 phases: 0 = everything, 1 = tile loads only
 };
 
@@ -129,6 +131,7 @@ struct Cache {
     void **vptrs_dev = nullptr;
     std::vector<CUtensorMap> maps_host;
     CUtensorMap *maps_dev = nullptr; // [n_layers][2] with the verify tile's box, then [n_layers][2] with the prefill tile's
+    float *qr = nullptr;             // [4][16][256] normalised and rotated queries of mkv_attn_step (stream-ordered)
     float *part_ml = nullptr;        // split-K scratch, shared by the layers (stream-ordered), grow-only
     float *part_o = nullptr;
     size_t scratch_pieces = 0;       // pieces (KV head x split) the scratch holds
@@ -158,6 +161,9 @@ mkv_status verify_setup_device();
 mkv_status launch_combine_shards(Ctx *ctx, const float *recs, int n_shards, uint32_t ntok, float *out);
 mkv_status launch_combine_exchange(Ctx *ctx, const float *slots, const uint32_t *flags, uint32_t epoch, int world, uint32_t ntok,
                                    float *out);
+mkv_status launch_step_prep(Ctx *ctx, mkv_fmt fmt, const float *qf, const float *kb, const float *vb, const float *q_norm,
+                            const float *k_norm, const float *tab, float eps, float *qr, void *kcache, void *vcache,
+                            uint32_t row_first, uint32_t capacity, uint32_t pos, uint32_t ntok);
 mkv_status launch_push_empty(Ctx *ctx, const PushInfo *push, uint32_t epoch, uint32_t world);
 // plans the split of the items so that the grid fills the SMs once
 void plan_items(Ctx *ctx, VerifyItem *items, int n);

@@ -186,6 +186,16 @@ class KvCache:
         """q_dmx + attn_dmx2 + attn_fd_combine (dmx.rs) / attn_fd (+combine): q, out f32 [ntok][16][256]."""
         check(_lib.lib().mkv_attn_verify(self._h, layer, first_pos, pos, q.shape[0], _ptr(q), _ptr(out)))
 
+    def attn_step(self, layer: int, first_pos: int, pos: int, qf: torch.Tensor, kb: torch.Tensor, vb: torch.Tensor,
+                  q_norm: torch.Tensor, k_norm: torch.Tensor, tab: torch.Tensor, out: torch.Tensor | None = None,
+                  out16: torch.Tensor | None = None, eps: float = 1e-6) -> None:
+        """The layer's step around the KV path in two launches (quad.rs:113-125): rmsnorm of q and k heads, rope2,
+        kv_rope2 + kv_copy of rows [pos, pos + ntok), the attention, attn_gate (out, f32) / attn_gate16 (out16, f16).
+        qf [ntok][16][512] (query | gate per head), kb [ntok][2][256], vb [ntok][512], norms [256], tab [ntok][64]."""
+        inp = _lib.StepIn(_ptr(qf), _ptr(kb), _ptr(vb), _ptr(q_norm), _ptr(k_norm), _ptr(tab), eps)
+        check(_lib.lib().mkv_attn_step(self._h, layer, first_pos, pos, qf.shape[0], C.byref(inp),
+                                       _ptr(out) if out is not None else None, _ptr(out16) if out16 is not None else None))
+
     def attn_verify_partial(self, layer: int, first_pos: int, pos: int, q: torch.Tensor, rec: torch.Tensor) -> None:
         """This shard's un-normalised record [64][258] for the step."""
         check(_lib.lib().mkv_attn_verify_partial(self._h, layer, first_pos, pos, q.shape[0], _ptr(q), _ptr(rec)))

@@ -464,3 +464,50 @@ uint64_t mko_root_key(const uint32_t *tok, size_t n) {
         }
     return h;
 }
+
+/* ---- the step either side of the KV path ------------------------------------------------------------------ */
+
+/* W/ops.wgsl:27-56 (rmsnorm, flag = 1, f1 = 1.0) */
+void mko_rmsnorm(const float *x, uint32_t rows, uint32_t n, uint32_t step_x, const float *w, float eps, float *y) {
+    for (uint32_t r = 0; r < rows; r++) {
+        const float *a = x + (size_t)r * step_x;
+        float partial[256];
+        for (uint32_t t = 0; t < 256; t++) { /* W/ops.wgsl:33-34 */
+            float s = 0.0f;
+            for (uint32_t i = t; i < n; i += 256u) { const float v = a[i]; s += v * v; }
+            partial[t] = s;
+        }
+        for (uint32_t m = 128u; m > 0u; m >>= 1) /* W/ops.wgsl:37-40 */
+            for (uint32_t t = 0; t < m; t++) partial[t] += partial[t + m];
+        const float scale = 1.0f / sqrtf(partial[0] / (float)n + eps); /* W/ops.wgsl:41 */
+        for (uint32_t i = 0; i < n; i++) { /* W/ops.wgsl:51-55 rms_val */
+            float v = a[i] * scale * 1.0f;
+            v = v * w[i];
+            y[(size_t)r * n + i] = v;
+        }
+    }
+}
+
+/* W/ops.wgsl:275-286 (rope2) */
+void mko_rope2(const float *x, uint32_t rows, uint32_t rows_per_tok, const float *tab, float *y) {
+    for (uint32_t r = 0; r < rows; r++) {
+        const float *a = x + (size_t)r * 256u, *tb = tab + (size_t)(r / rows_per_tok) * 64u;
+        float *o = y + (size_t)r * 256u;
+        for (uint32_t t = 0; t < 32u; t++) {
+            const float x1 = a[t], x2 = a[t + 32u], co = tb[t], si = tb[32u + t];
+            o[t] = x1 * co - x2 * si;
+            o[t + 32u] = x1 * si + x2 * co;
+        }
+        for (uint32_t t = 64u; t < 256u; t++) o[t] = a[t];
+    }
+}
+
+/* W/ops.wgsl:27 sigm and 171-177 attn_gate */
+void mko_attn_gate(const float *att, const float *qf, uint32_t ntok, float *out) {
+    const uint32_t n = ntok * 4096u;
+    for (uint32_t i = 0; i < n; i++) {
+        const uint32_t h = i / 256u, dd = i % 256u;
+        const float v = qf[(size_t)h * 512u + 256u + dd];
+        out[i] = att[i] * (1.0f / (1.0f + expf(-v)));
+    }
+}

@@ -50,6 +50,16 @@ void mko_append_k(int fmt, void *kcache, uint32_t pos, uint32_t ntok, const floa
 /* W/kv.wgsl:29-33 and W/ops.wgsl:141-145: V rows, convert and store */
 void mko_append_v(int fmt, void *vcache, uint32_t pos, uint32_t ntok, const float *vb);
 
+/* The step either side of the KV path (M/quad.rs:113-116,125,131):
+ * W/ops.wgsl:27-56 rmsnorm with flag 1 (weight) and scale 1: `rows` rows of n values, row r at x[r*step_x],
+ * y[r*n + i] = x * (1 / sqrt(sum(x^2)/n + eps)) * w[i]; the sum of squares in the shader's order (thread t adds
+ * elements t, t+256, ..., then the 256 partial sums are folded by halving strides). */
+void mko_rmsnorm(const float *x, uint32_t rows, uint32_t n, uint32_t step_x, const float *w, float eps, float *y);
+/* W/ops.wgsl:275-286 rope2: rows of 256 values, dims 0..63 rotated with the table of token r / rows_per_tok */
+void mko_rope2(const float *x, uint32_t rows, uint32_t rows_per_tok, const float *tab, float *y);
+/* W/ops.wgsl:171-177 attn_gate: out[i] = att[i] * sigmoid(qf[h*512 + 256 + d]), i = h*256 + d over ntok*16 heads */
+void mko_attn_gate(const float *att, const float *qf, uint32_t ntok, float *out);
+
 /* W/ops.wgsl:333-394 attn_fd_one for tokens 0..ntok-1 of a call at `pos`
  * (n = pos + 1), blocks of 128 positions from first_pos; partial records
  * [m, l, acc[256]] at ((tok*16+head)*nb+block)*258. nb = blocks allocated.

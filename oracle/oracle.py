@@ -55,6 +55,9 @@ def lib() -> C.CDLL:
         L.mko_snapshot.argtypes = [i32, vp, vp, u32, u32, vp]; L.mko_snapshot.restype = sz
         L.mko_restore.argtypes = [i32, vp, vp, u32, u32, vp]; L.mko_restore.restype = sz
         L.mko_root_key.argtypes = [vp, sz]; L.mko_root_key.restype = u64
+        L.mko_rmsnorm.argtypes = [vp, u32, u32, u32, vp, C.c_float, vp]
+        L.mko_rope2.argtypes = [vp, u32, u32, vp, vp]
+        L.mko_attn_gate.argtypes = [vp, vp, u32, vp]
         L.mko_threads.restype = i32
         _lib = L
     return _lib
@@ -168,6 +171,30 @@ def restore(fmt, kcs, vcs, p, src: np.ndarray) -> None:
     va = (C.c_void_p * n)(*[v.ctypes.data for v in vcs])
     r = lib().mko_restore(fmt, ka, va, n, p, _p(np.ascontiguousarray(src, np.uint8)))
     assert r == src.size
+
+
+def rmsnorm(x: np.ndarray, rows: int, n: int, step_x: int, w: np.ndarray, eps: float) -> np.ndarray:
+    """Rows of n values at stride step_x of the flat f32 array x, normalised and weighted (W/ops.wgsl:27-56)."""
+    x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1); w = np.ascontiguousarray(w, dtype=np.float32)
+    y = np.empty((rows, n), dtype=np.float32)
+    lib().mko_rmsnorm(_p(x), rows, n, step_x, _p(w), float(eps), _p(y))
+    return y
+
+
+def rope2(x: np.ndarray, rows_per_tok: int, tab: np.ndarray) -> np.ndarray:
+    """Rows of 256 values, dims 0..63 rotated with the table of token row // rows_per_tok (W/ops.wgsl:275-286)."""
+    x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1, 256); tab = np.ascontiguousarray(tab, dtype=np.float32)
+    y = np.empty_like(x)
+    lib().mko_rope2(_p(x), x.shape[0], rows_per_tok, _p(tab), _p(y))
+    return y
+
+
+def attn_gate(att: np.ndarray, qf: np.ndarray) -> np.ndarray:
+    """att [ntok][16][256] times the sigmoid of the gate half of qf [ntok][16][512] (W/ops.wgsl:171-177)."""
+    att = np.ascontiguousarray(att, dtype=np.float32); qf = np.ascontiguousarray(qf, dtype=np.float32)
+    out = np.empty_like(att)
+    lib().mko_attn_gate(_p(att), _p(qf), att.shape[0], _p(out))
+    return out
 
 
 def root_key(tokens) -> int:

@@ -325,6 +325,76 @@ def test_chained_launches_equal_synchronised_launches(ctx):
     cache.close()
 
 
+# ---------------------------------------------------------------- the step either side of the path ---------------
+
+@pytest.mark.parametrize("fmt", FMTS)
+@pytest.mark.parametrize("ntok,first", [(4, 0), (1, 0), (2, 700)])
+def test_fused_step_against_the_reference_dispatch_list(ctx, oracle, fmt, ntok, first):
+    """mkv_attn_step against the oracle run as the reference's dispatch list (quad.rs:113-125): rmsnorm of q and k
+    heads, rope2, kv_rope2 + kv_copy, attention, attn_gate. Cache rows bit for bit; output to the attention bar."""
+    pos, eps = 3000, 1e-6
+    cache = kv.KvCache(ctx, fmt, 2, 4096)
+    kc, vc = fill_both(oracle, cache, 1, pos, 81)
+    rng = np.random.default_rng(82 + ntok)
+    qf = (rng.standard_normal((ntok, 16, 512)) * 1.5).astype(np.float32)
+    kb = (rng.standard_normal((ntok, 2, 256)) * 0.7).astype(np.float32)
+    vb = rng.standard_normal((ntok, 512)).astype(np.float32)
+    qw = (1.0 + 0.1 * rng.standard_normal(256)).astype(np.float32)
+    kw = (1.0 + 0.1 * rng.standard_normal(256)).astype(np.float32)
+    tab = kv.rope_table(pos, ntok)
+    # the reference's order of operations on the CPU
+    qn = oracle.rmsnorm(qf, 16 * ntok, 256, 512, qw, eps)
+    kn = oracle.rmsnorm(kb, 2 * ntok, 256, 256, kw, eps)
+    qr = oracle.rope2(qn, 16, tab).reshape(ntok, 16, 256)
+    oracle.append(int(fmt), kc, vc, pos, kn.reshape(ntok, 2, 256), vb.reshape(ntok, 2, 256), tab)
+    att = oracle.attn_ref_f32(int(fmt), kc, vc, first, pos, qr)
+    want = oracle.attn_gate(att, qf)
+
+    out = torch.empty(ntok, 16, 256, device="cuda")
+    out16 = torch.empty(ntok, 16, 256, device="cuda", dtype=torch.float16)
+    n0 = ctx.launches
+    cache.attn_step(1, first, pos, dev(qf), dev(kb), dev(vb), dev(qw), dev(kw), dev(tab), out, out16, eps)
+    ctx.sync()
+    assert ctx.launches - n0 == 2  # nine dispatches of the reference in two launches
+    gk, gv = host_bits(cache, 1)
+    assert np.array_equal(gk[: pos + ntok], kc[: pos + ntok]) and np.array_equal(gv[: pos + ntok], vc[: pos + ntok])
+    assert len(cache) == pos + ntok
+    assert oracle.max_rel(out.cpu().numpy(), want) < TOL[fmt]
+    assert torch.equal(out16, out.half())
+    # the same through the separate operators: append of the normalised keys, then verify, must agree with the fused call
+    cache.truncate(pos)
+    cache.append(1, pos, dev(kn.reshape(ntok, 2, 256)), dev(vb.reshape(ntok, 2, 256)), dev(tab))
+    plain = torch.empty(ntok, 16, 256, device="cuda")
+    cache.attn_verify(1, first, pos, dev(qr), plain)
+    ctx.sync()
+    gated = oracle.attn_gate(plain.cpu().numpy(), qf)
+    assert oracle.max_rel(out.cpu().numpy(), gated) < 1e-6
+    # only one of the outputs
+    only16 = torch.empty_like(out16)
+    cache.truncate(pos)
+    cache.attn_step(1, first, pos, dev(qf), dev(kb), dev(vb), dev(qw), dev(kw), dev(tab), None, only16, eps)
+    ctx.sync()
+    assert torch.equal(only16, out16)
+    cache.close()
+
+
+def test_fused_step_argument_errors(ctx):
+    cache = kv.KvCache(ctx, kv.KvFormat.F16, 1, 4096)
+    z = lambda *s: torch.zeros(*s, device="cuda")
+    args = (z(4, 16, 512), z(4, 2, 256), z(4, 512), z(256), z(256), z(4, 64))
+    with pytest.raises(kv.MkvError):  # no output at all
+        cache.attn_step(0, 0, 0, *args, None, None)
+    with pytest.raises(kv.MkvError):  # a gap before the rows
+        cache.attn_step(0, 0, 10, *args, z(4, 16, 256))
+    with pytest.raises(kv.MkvError):  # past the context
+        cache.attn_step(0, 0, 4094, *args, z(4, 16, 256))
+    shard = kv.KvCache(ctx, kv.KvFormat.F16, 1, 8192, 4096, 4096)
+    with pytest.raises(kv.MkvError):  # shards have no gate of their own
+        shard.attn_step(0, 0, 0, *args, z(4, 16, 256))
+    shard.close()
+    cache.close()
+
+
 # ---------------------------------------------------------------- shards and batches ----------------------------
 
 @pytest.mark.parametrize("fmt", FMTS)

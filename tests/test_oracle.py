@@ -205,3 +205,32 @@ def test_snapshot_roundtrip_and_layout(oracle, fmt):
     for l in range(n_layers):
         assert np.array_equal(k2[l][:p], kcs[l][:p]) and not k2[l][p:].any()
         assert np.array_equal(v2[l][:p], vcs[l][:p]) and not v2[l][p:].any()
+
+
+def test_step_operators_around_the_path(oracle):
+    """rmsnorm / rope2 / attn_gate of the reference's dispatch list (quad.rs:113-116,125) as restated by the oracle."""
+    rng = np.random.default_rng(23)
+    ntok = 3
+    qf = (rng.standard_normal((ntok, 16, 512)) * 2.0).astype(np.float32)
+    w = (1.0 + 0.2 * rng.standard_normal(256)).astype(np.float32)
+    y = oracle.rmsnorm(qf, 16 * ntok, 256, 512, w, 1e-6)  # rows at stride 512: the query half of every head
+    x = qf[:, :, :256].reshape(-1, 256).astype(np.float64)
+    ref = x / np.sqrt((x * x).mean(axis=1, keepdims=True) + 1e-6) * w
+    assert np.abs(y - ref).max() < 2e-6 * np.abs(ref).max()
+    assert not np.array_equal(y, oracle.rmsnorm(qf[:, :, 256:].copy(), 16 * ntok, 256, 256, w, 1e-6))  # the stride matters
+    # rope2 on [rows][256] = the rotation the K writer applies before it converts (kv.wgsl:19-23)
+    tab = oracle.rope_tables(77, ntok)
+    kn = rng.standard_normal((ntok, 2, 256)).astype(np.float32)
+    rot = oracle.rope2(kn, 2, tab)
+    assert np.array_equal(rot[:, 64:], kn.reshape(-1, 256)[:, 64:])
+    kc, vc = oracle.new_cache(1, 128), oracle.new_cache(1, 128)
+    oracle.append(1, kc, vc, 5, kn, kn, tab)
+    assert np.array_equal(kc[5:5 + ntok].reshape(-1, 256), rot)
+    for t in range(ntok):  # a rotation keeps the norm of every (i, i + 32) pair
+        a, b = kn[t].reshape(2, 256), rot.reshape(ntok, 2, 256)[t]
+        assert np.allclose(a[:, :32] ** 2 + a[:, 32:64] ** 2, b[:, :32] ** 2 + b[:, 32:64] ** 2, rtol=1e-5)
+    # the gate reads the second half of each head's 512 values
+    att = rng.standard_normal((ntok, 16, 256)).astype(np.float32)
+    g = oracle.attn_gate(att, qf)
+    ref = att / (1.0 + np.exp(-qf[:, :, 256:].astype(np.float64)))
+    assert np.abs(g - ref).max() < 1e-6
