@@ -188,6 +188,22 @@ typedef struct {
 } mkv_verify_item;
 mkv_status mkv_attn_verify_batch(mkv_ctx *ctx, const mkv_verify_item *items, int n);
 
+/* Cache variants of the reference's second model (engine/crates/mechta/src/flint.rs:22-26,
+ * wgsl/flint_attn.wgsl:1-8), as options of the same kernels:
+ *  - ring cache: `ring_rows` rows per layer, position p lives in row p % ring_rows (flint_attn.wgsl:3,54,79), for
+ *    layers that only ever look back a window; ring_rows a multiple of 128, >= 1024. Appends, mkv_attn_step and the
+ *    verify calls work on it as long as the keys a call sees plus the rows of its step fit the ring; snapshots,
+ *    prefill and shards do not.
+ *  - sliding window: token t of a step at `pos` sees keys pos + t - window < key <= pos + t (flint.rs:22-23,
+ *    flint_attn.wgsl:82; window 513 there); 0 = no window.
+ *  - attention sinks: `sinks_dev` [16], one logit per query head that joins the softmax's maximum and sum and
+ *    never the output (flint_attn.wgsl:243-255, as ggml's soft_max with sinks); NULL = none.
+ * mkv_attn_verify_window works on ring and on ordinary (unsharded) caches. */
+mkv_status mkv_cache_create_ring(mkv_ctx *ctx, mkv_fmt fmt, int n_layers, uint32_t context_tokens, uint32_t ring_rows,
+                                 mkv_cache **out);
+mkv_status mkv_attn_verify_window(mkv_cache *c, int layer, uint32_t window, const float *sinks_dev, uint32_t pos,
+                                  uint32_t ntok, const float *q_dev, float *out_dev);
+
 /* The layer's whole step around the KV path in two launches. Replaces, for the ntok rows of a step, the nine
  * dispatches of engine/crates/mechta/src/quad.rs:113-125: rmsnorm of the query heads and of the key heads
  * (wgsl/ops.wgsl:27-56 with attn_q_norm / attn_k_norm), rope2 of the queries (ops.wgsl:275-286), kv_rope2 and

@@ -82,6 +82,8 @@ _SIGS = {
                                            C.c_void_p]),
     "mkv_combine_shards": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_uint32, C.c_void_p]),
     "mkv_attn_verify_batch": (C.c_int, [C.c_void_p, C.POINTER(VerifyItem), C.c_int]),
+    "mkv_cache_create_ring": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_uint32, C.c_uint32, C.POINTER(C.c_void_p)]),
+    "mkv_attn_verify_window": (C.c_int, [C.c_void_p, C.c_int, C.c_uint32, C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p]),
     "mkv_attn_step": (C.c_int, [C.c_void_p, C.c_int, C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(StepIn), C.c_void_p, C.c_void_p]),
     "mkv_attn_prefill": (C.c_int, [C.c_void_p, C.c_int, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p]),
     "mkv_snapshot_bytes": (C.c_size_t, [C.c_void_p, C.c_uint32]),

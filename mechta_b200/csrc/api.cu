@@ -143,7 +143,11 @@ static mkv_status fill_item(Cache *c, int layer, uint32_t first_pos, uint32_t po
         set_error("first_pos %u > pos %u: token 0 would see no key", first_pos, pos);
         return MKV_ERR_INVALID;
     }
-    const uint32_t shard_end = c->shard_first + c->capacity;
+    const uint32_t shard_end = c->ring ? c->context : c->shard_first + c->capacity;
+    if (c->ring && partial) {
+        set_error("a ring cache is not sharded");
+        return MKV_ERR_UNSUPPORTED;
+    }
     if (!partial && !c->whole) {
         set_error("this cache is the shard [%u, %u) of a context of %u: use mkv_attn_verify_partial", c->shard_first, shard_end,
                   c->context);
@@ -169,6 +173,7 @@ static mkv_status fill_item(Cache *c, int layer, uint32_t first_pos, uint32_t po
     it->row0 = c->shard_first;
     it->key_lo = c->shard_first;
     it->key_hi = shard_end;
+    it->ring = c->ring;
     it->partial = partial ? 1u : 0u;
     it->phase = measure_phase();
     it->safe_below = std::min(pos, c->last_write_pos);
@@ -204,11 +209,28 @@ static mkv_status place_scratch(Cache *const *caches, VerifyItem *items, int n) 
     return MKV_OK;
 }
 
+// Window and sinks on a filled item: the key range shrinks to what token 0 still sees; on a ring cache every visible
+// key and every row of the step must own its row.
+static mkv_status apply_window(Cache *c, VerifyItem *it, uint32_t window, const float *sinks) {
+    it->win = window;
+    it->sinks = sinks;
+    const uint32_t T = c->fmt == MKV_F16 ? TILE : TILE32;
+    const uint32_t lo = lowest_key(*it, 0), hi = it->pos + it->ntok;
+    if (c->ring && hi - lo > c->ring) {
+        set_error("keys [%u, %u) do not fit a ring of %u rows: pass a window of at most %u", lo, hi, c->ring, c->ring - it->ntok + 1u);
+        return MKV_ERR_CAPACITY;
+    }
+    it->tile_begin = lo / T;
+    it->tile_end = (hi + T - 1) / T;
+    return MKV_OK;
+}
+
 static mkv_status verify_common(Cache *c, int layer, uint32_t first_pos, uint32_t pos, uint32_t ntok, const float *q,
                                 float *out, bool partial) {
     VerifyItem it;
     mkv_status st = fill_item(c, layer, first_pos, pos, ntok, q, out, partial, &it);
     if (st != MKV_OK) return st;
+    if (c->ring && (st = apply_window(c, &it, 0, nullptr)) != MKV_OK) return st;
     if ((st = use_device(c->ctx)) != MKV_OK) return st;
     plan_items(c->ctx, &it, 1);
     Cache *cc[1] = {c};
@@ -384,8 +406,8 @@ uint64_t mkv_need_bytes(uint32_t ctx_tokens, mkv_fmt fmt, int n_layers) {
     return kv + partials;
 }
 
-mkv_status mkv_cache_create(mkv_ctx *h, mkv_fmt fmt, int n_layers, uint32_t context, uint32_t shard_first,
-                            uint32_t shard_tokens, mkv_cache **out) {
+static mkv_status cache_create_common(mkv_ctx *h, mkv_fmt fmt, int n_layers, uint32_t context, uint32_t shard_first,
+                                      uint32_t shard_tokens, uint32_t ring, mkv_cache **out) {
     Ctx *ctx = reinterpret_cast<Ctx *>(h);
     if (!ctx || !out || ctx->closing) {
         set_error("null argument");
@@ -405,8 +427,12 @@ mkv_status mkv_cache_create(mkv_ctx *h, mkv_fmt fmt, int n_layers, uint32_t cont
         set_error("context %u: must be a multiple of 1024 between %d and %d", context, MKV_CTX_MIN, MKV_CTX_MAX);
         return MKV_ERR_INVALID;
     }
+    if (ring && (ring % 128u != 0 || ring < 1024u || ring > context)) {
+        set_error("ring of %u rows: must be a multiple of 128, at least 1024 and at most the context %u", ring, context);
+        return MKV_ERR_INVALID;
+    }
     const bool whole = shard_tokens == 0;
-    const uint32_t capacity = whole ? context : shard_tokens;
+    const uint32_t capacity = ring ? ring : (whole ? context : shard_tokens);
     if (whole ? shard_first != 0
               : (capacity % 64 != 0 || shard_first % 64 != 0 || (uint64_t)shard_first + capacity > (uint64_t)context)) {
         set_error("shard [%u, +%u): first row and size must be multiples of 64 inside the context %u", shard_first,
@@ -422,6 +448,7 @@ mkv_status mkv_cache_create(mkv_ctx *h, mkv_fmt fmt, int n_layers, uint32_t cont
     c->n_layers = n_layers;
     c->context = context;
     c->capacity = capacity;
+    c->ring = ring;
     c->shard_first = shard_first;
     c->whole = whole;
     ctx->live_caches++;
@@ -478,6 +505,19 @@ mkv_status mkv_cache_create(mkv_ctx *h, mkv_fmt fmt, int n_layers, uint32_t cont
     }
     *out = reinterpret_cast<mkv_cache *>(c);
     return MKV_OK;
+}
+
+mkv_status mkv_cache_create(mkv_ctx *h, mkv_fmt fmt, int n_layers, uint32_t context, uint32_t shard_first,
+                            uint32_t shard_tokens, mkv_cache **out) {
+    return cache_create_common(h, fmt, n_layers, context, shard_first, shard_tokens, 0, out);
+}
+
+mkv_status mkv_cache_create_ring(mkv_ctx *h, mkv_fmt fmt, int n_layers, uint32_t context, uint32_t ring_rows, mkv_cache **out) {
+    if (ring_rows == 0) {
+        set_error("ring_rows must not be 0");
+        return MKV_ERR_INVALID;
+    }
+    return cache_create_common(h, fmt, n_layers, context, 0, 0, ring_rows, out);
 }
 
 void mkv_cache_destroy(mkv_cache *h) {
@@ -568,12 +608,16 @@ static mkv_status append_common(Cache *c, int layer0, int n_layers, uint32_t pos
         set_error("rows [%u, %u) do not fit the context of %u rows", pos, (uint32_t)end, c->context);
         return MKV_ERR_CAPACITY;
     }
+    if (c->ring && ntok > c->ring) {
+        set_error("a ring cache of %u rows cannot take %u rows in one call", c->ring, ntok);
+        return MKV_ERR_CAPACITY;
+    }
     mkv_status st = use_device(c->ctx);
     if (st != MKV_OK) return st;
     st = launch_append(c->ctx, c->fmt, c->kptrs_dev + layer0, c->vptrs_dev + layer0, n_layers, (size_t)ntok * ROW,
-                       c->shard_first, c->capacity, pos, ntok, k, v, tab, 3u);
+                       c->shard_first, c->capacity, c->ring, pos, ntok, k, v, tab, 3u);
     if (st != MKV_OK) return st;
-    c->len = (uint32_t)std::min<uint64_t>(end, shard_end);
+    c->len = c->ring ? (uint32_t)end : (uint32_t)std::min<uint64_t>(end, shard_end);
     if (c->len < c->shard_first) c->len = c->shard_first;
     c->last_write_pos = pos;
     return MKV_OK;
@@ -607,6 +651,10 @@ mkv_status mkv_truncate(mkv_cache *h, uint32_t new_len, int scrub) {
         set_error("cannot truncate to %u: only %u rows are valid", new_len, c->len);
         return MKV_ERR_STATE;
     }
+    if (scrub && c->ring) {
+        set_error("a ring cache has no scrub: its rows are reused by later positions");
+        return MKV_ERR_UNSUPPORTED;
+    }
     const uint32_t old = c->len;
     c->len = std::max(new_len, std::min(c->shard_first, old));
     if (scrub && old > c->len) {
@@ -625,6 +673,20 @@ mkv_status mkv_truncate(mkv_cache *h, uint32_t new_len, int scrub) {
 
 mkv_status mkv_attn_verify(mkv_cache *h, int layer, uint32_t first_pos, uint32_t pos, uint32_t ntok, const float *q, float *out) {
     return verify_common(reinterpret_cast<Cache *>(h), layer, first_pos, pos, ntok, q, out, false);
+}
+
+mkv_status mkv_attn_verify_window(mkv_cache *h, int layer, uint32_t window, const float *sinks, uint32_t pos, uint32_t ntok,
+                                  const float *q, float *out) {
+    Cache *c = reinterpret_cast<Cache *>(h);
+    VerifyItem it;
+    mkv_status st = fill_item(c, layer, 0, pos, ntok, q, out, false, &it);
+    if (st != MKV_OK) return st;
+    if ((st = apply_window(c, &it, window, sinks)) != MKV_OK) return st;
+    if ((st = use_device(c->ctx)) != MKV_OK) return st;
+    plan_items(c->ctx, &it, 1);
+    Cache *cc[1] = {c};
+    if ((st = place_scratch(cc, &it, 1)) != MKV_OK) return st;
+    return launch_verify(c->ctx, c->fmt, &it, 1, false, &c->maps_host[2 * layer], &c->maps_host[2 * layer + 1]);
 }
 
 mkv_status mkv_attn_step(mkv_cache *h, int layer, uint32_t first_pos, uint32_t pos, uint32_t ntok, const mkv_step_in *in,
@@ -677,7 +739,7 @@ mkv_status mkv_attn_step(mkv_cache *h, int layer, uint32_t first_pos, uint32_t p
     it.gate = in->qf_dev;
     it.out16 = ag16;
     st = launch_step_prep(c->ctx, c->fmt, in->qf_dev, in->kb_dev, in->vb_dev, in->q_norm_dev, in->k_norm_dev, in->rope_tab_dev,
-                          in->eps, c->qr, c->k[layer], c->v[layer], c->shard_first, c->capacity, pos, ntok);
+                          in->eps, c->qr, c->k[layer], c->v[layer], c->shard_first, c->capacity, c->ring, pos, ntok);
     if (st != MKV_OK) return st;
     plan_items(c->ctx, &it, 1);
     Cache *cc[1] = {c};
@@ -846,6 +908,7 @@ mkv_status mkv_attn_verify_batch(mkv_ctx *h, const mkv_verify_item *items, int n
         mkv_status st = fill_item(c, items[i].layer, items[i].first_pos, items[i].pos, items[i].ntok, items[i].q_dev,
                                   items[i].out_dev, false, &its[i]);
         if (st != MKV_OK) return st;
+        if (c->ring && (st = apply_window(c, &its[i], 0, nullptr)) != MKV_OK) return st;
         caches[i] = c;
     }
     mkv_status st = use_device(ctx);
@@ -861,6 +924,10 @@ mkv_status mkv_attn_prefill(mkv_cache *h, int layer, uint32_t first_pos, uint32_
     if (!c || !q || !out || layer < 0 || layer >= c->n_layers) {
         set_error("bad argument to mkv_attn_prefill");
         return MKV_ERR_INVALID;
+    }
+    if (c->ring) {
+        set_error("not available on a ring cache");
+        return MKV_ERR_UNSUPPORTED;
     }
     if (ntok < 1 || ntok > 4096) {
         set_error("ntok %u outside [1, 4096]", ntok);
@@ -941,6 +1008,10 @@ mkv_status mkv_snapshot(mkv_cache *h, uint32_t p, void *dst, size_t cap, size_t 
         set_error("null argument");
         return MKV_ERR_INVALID;
     }
+    if (c->ring) {
+        set_error("not available on a ring cache");
+        return MKV_ERR_UNSUPPORTED;
+    }
     {
         const uint32_t upto = std::min(p, c->shard_first + c->capacity); // the rows of [0, p) held here
         if (upto > c->shard_first && upto > c->len) {
@@ -997,6 +1068,10 @@ mkv_status mkv_restore(mkv_cache *h, uint32_t p, const void *src, size_t bytes) 
     if (!c || (!src && bytes != 0)) {
         set_error("null argument");
         return MKV_ERR_INVALID;
+    }
+    if (c->ring) {
+        set_error("not available on a ring cache");
+        return MKV_ERR_UNSUPPORTED;
     }
     const uint32_t end = c->shard_first + c->capacity;
     if (p > c->context) {
@@ -1090,7 +1165,7 @@ mkv_status mkv_dispatch(mkv_cache *h, int layer, const char *op, const uint32_t 
         mkv_status st = use_device(c->ctx);
         if (st != MKV_OK) return st;
         return launch_append(c->ctx, c->fmt, c->kptrs_dev + layer, c->vptrs_dev + layer, 1, (size_t)ntok * ROW,
-                             c->shard_first, c->capacity, pos, ntok, (const float *)in0, (const float *)in0,
+                             c->shard_first, c->capacity, c->ring, pos, ntok, (const float *)in0, (const float *)in0,
                              (const float *)in1, 1u);
     }
     if (is("kv_copy") || is("copy")) {
@@ -1115,7 +1190,7 @@ mkv_status mkv_dispatch(mkv_cache *h, int layer, const char *op, const uint32_t 
         mkv_status st = use_device(c->ctx);
         if (st != MKV_OK) return st;
         st = launch_append(c->ctx, c->fmt, c->kptrs_dev + layer, c->vptrs_dev + layer, 1, (size_t)ntok * ROW, c->shard_first,
-                           c->capacity, pos, ntok, (const float *)in0, (const float *)in0, nullptr, 2u);
+                           c->capacity, c->ring, pos, ntok, (const float *)in0, (const float *)in0, nullptr, 2u);
         // the V writer is the second of the pair (M/quad.rs:116-117): the rows are now complete
         if (st == MKV_OK) c->len = pos + ntok;
         c->last_write_pos = 0;

@@ -8,14 +8,20 @@
 // with each product and the sum/difference rounded to f32 on its own (no FMA contraction), then
 // round-to-nearest-even to f16 for the f16 cache. V is converted and stored (W/kv.wgsl:29-33).
 #include "internal.cuh"
+#include "ptx.cuh"
 
 namespace mkv {
 
 template <bool F16>
 __global__ void __launch_bounds__(256)
 append_kernel(void *const *__restrict__ kbufs, void *const *__restrict__ vbufs, int n_layers, size_t layer_stride,
-              uint32_t row_first, uint32_t capacity, uint32_t pos, uint32_t ntok, const float *__restrict__ k,
-              const float *__restrict__ v, const float *__restrict__ tab, uint32_t which) {
+              uint32_t row_first, uint32_t capacity, uint32_t ring, uint32_t pos, uint32_t ntok,
+              const float *__restrict__ k, const float *__restrict__ v, const float *__restrict__ tab, uint32_t which) {
+    // Programmatic dependent launch on both sides: the attention kernel behind this one may set itself up and load
+    // tiles below `pos` meanwhile; this kernel touches nothing before the kernel in front has finished (its inputs
+    // may come from it, and the rows it overwrites after a rollback may still be read by the attention in front).
+    ptx::pdl_launch_dependents();
+    ptx::pdl_wait();
     // one thread = 8 consecutive elements; per (layer, token): 64 groups of K then 64 groups of V
     const size_t gid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t total = (size_t)n_layers * ntok * 128u;
@@ -26,8 +32,8 @@ append_kernel(void *const *__restrict__ kbufs, void *const *__restrict__ vbufs, 
     const uint32_t tok = (uint32_t)((gid >> 7) % ntok);
     const uint32_t layer = (uint32_t)((gid >> 7) / ntok);
     const uint32_t gpos = pos + tok;
-    if (gpos < row_first || gpos - row_first >= capacity) return; // row belongs to another shard
-    const size_t row = gpos - row_first;
+    if (!ring && (gpos < row_first || gpos - row_first >= capacity)) return; // row belongs to another shard
+    const size_t row = ring ? gpos % ring : gpos - row_first; // ring cache: row = position % ring (W/flint_attn.wgsl:3)
     const uint32_t e0 = g * 8u; // element inside the position: kvh * 256 + d
     const float *src = (is_v ? v : k) + layer * layer_stride + (size_t)tok * ROW;
     float x[8];
@@ -91,18 +97,25 @@ mkv_status append_setup_device() {
 }
 
 mkv_status launch_append(Ctx *ctx, mkv_fmt fmt, void *const *kbufs, void *const *vbufs, int n_layers,
-                         size_t layer_stride_in, uint32_t row_first, uint32_t capacity, uint32_t pos, uint32_t ntok,
-                         const float *k, const float *v, const float *tab, uint32_t which) {
+                         size_t layer_stride_in, uint32_t row_first, uint32_t capacity, uint32_t ring, uint32_t pos,
+                         uint32_t ntok, const float *k, const float *v, const float *tab, uint32_t which) {
     const size_t total = (size_t)n_layers * ntok * 128u;
-    const unsigned blocks = (unsigned)((total + 255u) / 256u);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)((total + 255u) / 256u));
+    cfg.blockDim = dim3(256);
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = ctx->pdl ? 1 : 0;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
     if (fmt == MKV_F16)
-        append_kernel<true><<<blocks, 256, 0, ctx->stream>>>(kbufs, vbufs, n_layers, layer_stride_in, row_first, capacity,
-                                                             pos, ntok, k, v, tab, which);
+        MKV_CUDA(cudaLaunchKernelEx(&cfg, append_kernel<true>, kbufs, vbufs, n_layers, layer_stride_in, row_first, capacity, ring, pos,
+                                    ntok, k, v, tab, which));
     else
-        append_kernel<false><<<blocks, 256, 0, ctx->stream>>>(kbufs, vbufs, n_layers, layer_stride_in, row_first,
-                                                              capacity, pos, ntok, k, v, tab, which);
+        MKV_CUDA(cudaLaunchKernelEx(&cfg, append_kernel<false>, kbufs, vbufs, n_layers, layer_stride_in, row_first, capacity, ring, pos,
+                                    ntok, k, v, tab, which));
     ctx->launches++;
-    MKV_CUDA(cudaGetLastError());
     return MKV_OK;
 }
 

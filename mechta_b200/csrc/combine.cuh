@@ -37,7 +37,8 @@ struct FinishSmem {
 };
 
 // One row (kvh * 32 + row) of one item, by all NT threads of the CTA.
-template <int NT>
+// EXT = false compiles the sink handling out (the kernels of the plain path are instantiated without it).
+template <int NT, bool EXT = true>
 __device__ __forceinline__ void merge_row(const VerifyItem &it, uint32_t r, FinishSmem &sm) {
     constexpr int GROUPS = NT / 64;
     constexpr int NW = NT / 32;
@@ -82,7 +83,9 @@ __device__ __forceinline__ void merge_row(const VerifyItem &it, uint32_t r, Fini
         float y = tid < NW ? sm.red[tid] : NEG_BIG;
 #pragma unroll
         for (int sh = 16; sh > 0; sh >>= 1) y = fmaxf(y, __shfl_xor_sync(0xffffffffu, y, sh));
-        if (tid == 0) sm.M = y;
+        // a sink logit of the row's head joins the maximum and the sum, never the output (ggml's soft_max with sinks,
+        // W/flint_attn.wgsl:243-255)
+        if (tid == 0) sm.M = (EXT && it.sinks && !it.partial) ? fmaxf(y, it.sinks[head]) : y;
     }
     __syncthreads();
     M = sm.M;
@@ -97,7 +100,7 @@ __device__ __forceinline__ void merge_row(const VerifyItem &it, uint32_t r, Fini
         float y = tid < NW ? sm.red[tid] : 0.0f;
 #pragma unroll
         for (int sh = 16; sh > 0; sh >>= 1) y += __shfl_xor_sync(0xffffffffu, y, sh);
-        if (tid == 0) sm.tot = y;
+        if (tid == 0) sm.tot = (EXT && it.sinks && !it.partial) ? y + expf(it.sinks[head] - sm.M) : y;
     }
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (uint32_t s0 = grp; s0 < ns; s0 += GROUPS * (uint32_t)RND) {
@@ -160,7 +163,7 @@ __device__ __forceinline__ void merge_row(const VerifyItem &it, uint32_t r, Fini
 
 // Called by every thread of every CTA of an item after the CTA's piece has been written to global memory.
 // `sm` must not alias anything still in use. Returns after this CTA's share of the merge (possibly none).
-template <int NT>
+template <int NT, bool EXT = true>
 __device__ __forceinline__ void finish_item(const VerifyItem &it, FinishSmem &sm, uint32_t *status) {
     const uint32_t total = 2u * it.nsplit;
     __syncthreads(); // every thread's part of the piece precedes thread 0's release below
@@ -194,7 +197,7 @@ __device__ __forceinline__ void finish_item(const VerifyItem &it, FinishSmem &sm
     }
     __syncthreads();
     if (!sm.ok) return;
-    for (uint32_t r = ticket - (total - R); r < 64u; r += R) merge_row<NT>(it, r, sm);
+    for (uint32_t r = ticket - (total - R); r < 64u; r += R) merge_row<NT, EXT>(it, r, sm);
 #ifdef MKV_TRACE
     __syncthreads();
     if (threadIdx.x == 0) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(sm.tr[2]));

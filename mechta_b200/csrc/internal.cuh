@@ -69,6 +69,9 @@ struct VerifyItem {
     uint32_t push_world;  // number of ranks (host copy of push->world)
     uint32_t push_epoch, push_base; // the exchange's call number; value of rows_done before this launch
     uint32_t safe_below; // keys below this were not written by the kernel launched just before this one
+    uint32_t ring;       // rows of a ring cache (row = position % ring), 0 = rows are positions minus row0
+    uint32_t win;        // sliding window: token t sees keys > pos + t - win (0 = no window)
+    const float *sinks;  // final mode only: [16] per-head sink logits that join the softmax's max and sum, or null
     const float *gate;   // final mode only: [ntok][16][512] with the output gate in the second half of each head, or null
     void *out16;         // final mode only: the output once more as f16 [ntok][16][256], or null
     uint32_t phase;     // measurement only, as the reference's p.f1 phases: 0 = everything, 1 = tile loads only
@@ -76,6 +79,15 @@ struct VerifyItem {
 
 // What a single (non-batched) launch carries in the kernel's parameter space: the item and its two tensor
 // maps, so that the TMA unit does not have to fetch the maps from global memory first.
+// Row of the cache that holds absolute position `key`.
+__host__ __device__ inline uint32_t cache_row(const VerifyItem &it, uint32_t key) { return it.ring ? key % it.ring : key - it.row0; }
+// Lowest key token t of the step sees: the call's first position, the shard's first row, the window.
+__host__ __device__ inline uint32_t lowest_key(const VerifyItem &it, uint32_t t) {
+    uint32_t lo = it.first_pos > it.key_lo ? it.first_pos : it.key_lo;
+    if (it.win && it.pos + t + 1u > it.win && it.pos + t + 1u - it.win > lo) lo = it.pos + t + 1u - it.win;
+    return lo;
+}
+
 struct VerifyLaunch {
     VerifyItem item;
     alignas(64) CUtensorMap kmap;
@@ -119,6 +131,7 @@ struct Cache {
     mkv_fmt fmt = MKV_F16;
     int n_layers = 0;
     uint32_t context = 0;  // tokens of the whole sequence's context
+    uint32_t ring = 0;               // rows of a ring cache (then capacity == ring), 0 otherwise
     uint32_t capacity = 0; // rows held here
     uint32_t shard_first = 0;
     bool whole = true;     // holds the whole context (not a sequence shard)
@@ -152,8 +165,9 @@ struct Exchange {
 
 // ---- launchers (defined in the .cu files) ---------------------------------------------------------------
 mkv_status launch_append(Ctx *ctx, mkv_fmt fmt, void *const *kbufs, void *const *vbufs, int n_layers,
-                         size_t layer_stride_in, uint32_t row_first, uint32_t capacity, uint32_t pos, uint32_t ntok,
-                         const float *k, const float *v, const float *tab, uint32_t which /*1 = K, 2 = V, 3 = both*/);
+                         size_t layer_stride_in, uint32_t row_first, uint32_t capacity, uint32_t ring, uint32_t pos,
+                         uint32_t ntok, const float *k, const float *v, const float *tab,
+                         uint32_t which /*1 = K, 2 = V, 3 = both*/);
 // items_host[0..n) are planned; batch = false: n == 1 and the item travels in the kernel's parameter space
 mkv_status launch_verify(Ctx *ctx, mkv_fmt fmt, VerifyItem *items_host, int n, bool batch, const CUtensorMap *kmap_host,
                          const CUtensorMap *vmap_host);
@@ -163,7 +177,7 @@ mkv_status launch_combine_exchange(Ctx *ctx, const float *slots, const uint32_t 
                                    float *out);
 mkv_status launch_step_prep(Ctx *ctx, mkv_fmt fmt, const float *qf, const float *kb, const float *vb, const float *q_norm,
                             const float *k_norm, const float *tab, float eps, float *qr, void *kcache, void *vcache,
-                            uint32_t row_first, uint32_t capacity, uint32_t pos, uint32_t ntok);
+                            uint32_t row_first, uint32_t capacity, uint32_t ring, uint32_t pos, uint32_t ntok);
 mkv_status launch_push_empty(Ctx *ctx, const PushInfo *push, uint32_t epoch, uint32_t world);
 // plans the split of the items so that the grid fills the SMs once
 void plan_items(Ctx *ctx, VerifyItem *items, int n);

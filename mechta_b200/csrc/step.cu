@@ -23,7 +23,7 @@ __global__ void __launch_bounds__(256)
 step_prep_kernel(const float *__restrict__ qf, const float *__restrict__ kb, const float *__restrict__ vb,
                  const float *__restrict__ q_norm, const float *__restrict__ k_norm, const float *__restrict__ tab, float eps,
                  float *__restrict__ qr, void *__restrict__ kcache, void *__restrict__ vcache, uint32_t row_first,
-                 uint32_t capacity, uint32_t pos) {
+                 uint32_t capacity, uint32_t ring, uint32_t pos) {
     __shared__ float partial[256];
     __shared__ float row[256];
     // Programmatic dependent launch on both sides: the attention kernel behind this one may set itself up and load
@@ -33,8 +33,8 @@ step_prep_kernel(const float *__restrict__ qf, const float *__restrict__ kb, con
     ptx::pdl_wait();
     const uint32_t t = threadIdx.x, tok = blockIdx.x / 20u, r = blockIdx.x % 20u;
     const uint32_t gpos = pos + tok;
-    const bool held = gpos >= row_first && gpos - row_first < capacity; // the row belongs to this shard
-    const size_t crow = held ? (size_t)(gpos - row_first) * ROW : 0;
+    const bool held = ring || (gpos >= row_first && gpos - row_first < capacity); // the row belongs to this shard
+    const size_t crow = held ? (size_t)(ring ? gpos % ring : gpos - row_first) * ROW : 0;
     if (r >= 18u) { // V: convert and store (W/kv.wgsl:29-33)
         if (!held) return;
         const uint32_t e = (r - 18u) * 256u + t;
@@ -75,7 +75,7 @@ step_prep_kernel(const float *__restrict__ qf, const float *__restrict__ kb, con
 
 mkv_status launch_step_prep(Ctx *ctx, mkv_fmt fmt, const float *qf, const float *kb, const float *vb, const float *q_norm,
                             const float *k_norm, const float *tab, float eps, float *qr, void *kcache, void *vcache,
-                            uint32_t row_first, uint32_t capacity, uint32_t pos, uint32_t ntok) {
+                            uint32_t row_first, uint32_t capacity, uint32_t ring, uint32_t pos, uint32_t ntok) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(20u * ntok);
     cfg.blockDim = dim3(256);
@@ -87,10 +87,10 @@ mkv_status launch_step_prep(Ctx *ctx, mkv_fmt fmt, const float *qf, const float 
     cfg.numAttrs = 1;
     if (fmt == MKV_F16)
         MKV_CUDA(cudaLaunchKernelEx(&cfg, step_prep_kernel<true>, qf, kb, vb, q_norm, k_norm, tab, eps, qr, kcache, vcache, row_first,
-                                    capacity, pos));
+                                    capacity, ring, pos));
     else
         MKV_CUDA(cudaLaunchKernelEx(&cfg, step_prep_kernel<false>, qf, kb, vb, q_norm, k_norm, tab, eps, qr, kcache, vcache, row_first,
-                                    capacity, pos));
+                                    capacity, ring, pos));
     ctx->launches++;
     return MKV_OK;
 }

@@ -68,7 +68,7 @@ verify_f16_kernel(const VerifyItem *__restrict__ items, int n_items, const __gri
     auto issue = [&](uint32_t j) { // thread 0 only: tile j of this CTA into stage j % NST
         const uint32_t s = j % V16_NST, bar = bar0 + 8u * s;
         const uint32_t dst = smem_base + s * V16_STAGE;
-        const int y = (int)((t0 + j) * TILE - it.row0);
+        const int y = (int)cache_row(it, (t0 + j) * TILE);
         const int x = (int)(kvh * 256u);
         mbar_expect_tx(bar, V16_STAGE);
 #pragma unroll
@@ -141,7 +141,7 @@ verify_f16_kernel(const VerifyItem *__restrict__ items, int n_items, const __gri
     const uint32_t srow = tid >> 3, seg = tid & 7u;
     const uint32_t stok = srow >> 3;
     const uint32_t vis = min(it.pos + 1u + stok, it.key_hi);
-    const uint32_t klo = max(it.first_pos, it.key_lo);
+    const uint32_t klo = lowest_key(it, stok);
     float m_run = NEG_BIG, l_run = 0.0f;
     float *S = reinterpret_cast<float *>(smem + V16_OFF_S);
     float *cfs = reinterpret_cast<float *>(smem + V16_OFF_CF);
@@ -487,9 +487,11 @@ mkv_status launch_combine_shards(Ctx *ctx, const float *recs, int n_shards, uint
     return MKV_OK;
 }
 
-mkv_status launch_verify_f32(Ctx *ctx, const VerifyItem *items_dev, int n, const VerifyLaunch &single, uint32_t total_ctas);
+mkv_status launch_verify_f32(Ctx *ctx, const VerifyItem *items_dev, int n, const VerifyLaunch &single, uint32_t total_ctas,
+                             bool ext);
 mkv_status verify_f32_setup_device();
-mkv_status launch_verify_f16_tc(Ctx *ctx, const VerifyItem *items_dev, int n, const VerifyLaunch &single, uint32_t total_ctas);
+mkv_status launch_verify_f16_tc(Ctx *ctx, const VerifyItem *items_dev, int n, const VerifyLaunch &single, uint32_t total_ctas,
+                                bool ext);
 mkv_status verify_tc_setup_device();
 
 // MKV_VERIFY=mma selects the warp-MMA kernel of this file for the f16 cache; the default is the tcgen05 kernel.
@@ -520,8 +522,9 @@ mkv_status launch_verify(Ctx *ctx, mkv_fmt fmt, VerifyItem *items_host, int n, b
         return MKV_ERR_INVALID;
     }
     uint32_t total = 0;
-    bool any_empty = false;
+    bool any_empty = false, ext = false; // ext: some item uses ring rows, a window or sinks
     for (int i = 0; i < n; i++) {
+        ext |= items_host[i].ring != 0 || items_host[i].win != 0 || items_host[i].sinks != nullptr;
         total += 2u * items_host[i].nsplit;
         any_empty |= items_host[i].nsplit == 0;
         items_host[i].counter = ctx->counters_dev + i;
@@ -565,7 +568,7 @@ mkv_status launch_verify(Ctx *ctx, mkv_fmt fmt, VerifyItem *items_host, int n, b
     }
     if (total > 0) {
         if (fmt == MKV_F16 && verify_use_tc()) {
-            mkv_status st = launch_verify_f16_tc(ctx, items_dev, n, single, total);
+            mkv_status st = launch_verify_f16_tc(ctx, items_dev, n, single, total, ext);
             if (st != MKV_OK) return st;
         } else if (fmt == MKV_F16) {
             // programmatic dependent launch: this kernel's prologue and first tile loads may overlap the tail
@@ -583,7 +586,7 @@ mkv_status launch_verify(Ctx *ctx, mkv_fmt fmt, VerifyItem *items_host, int n, b
             MKV_CUDA(cudaLaunchKernelEx(&cfg, verify_f16_kernel, items_dev, n, single, ctx->dev_status));
             ctx->launches++;
         } else {
-            mkv_status st = launch_verify_f32(ctx, items_dev, n, single, total);
+            mkv_status st = launch_verify_f32(ctx, items_dev, n, single, total, ext);
             if (st != MKV_OK) return st;
         }
         for (int i = 0; i < n; i++) ctx->counter_base[i] += 2u * items_host[i].nsplit;

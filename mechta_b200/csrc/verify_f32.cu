@@ -55,6 +55,7 @@ __device__ __forceinline__ void split8(const float (&x)[8], uint4 &hi, uint4 &lo
     lo = make_uint4(l[0], l[1], l[2], l[3]);
 }
 
+template <bool EXT> // ring rows, sliding window and sinks compiled in or out, as in verify_tc.cu
 __global__ void __launch_bounds__(256, 1)
 verify_f32_kernel(const VerifyItem *__restrict__ items, int n_items, const __grid_constant__ VerifyLaunch single,
                   uint32_t *__restrict__ status) {
@@ -91,7 +92,7 @@ verify_f32_kernel(const VerifyItem *__restrict__ items, int n_items, const __gri
     auto issue = [&](uint32_t j) {
         const uint32_t s = j % V32_NST, bar = bar0 + 8u * s;
         const uint32_t dst = smem_base + s * V32_STAGE;
-        const int y = (int)((t0 + j) * TILE32 - it.row0);
+        const int y = (int)(EXT ? cache_row(it, (t0 + j) * TILE32) : (t0 + j) * TILE32 - it.row0);
         const int x = (int)(kvh * 256u);
         mbar_expect_tx(bar, V32_STAGE);
 #pragma unroll
@@ -159,7 +160,7 @@ verify_f32_kernel(const VerifyItem *__restrict__ items, int n_items, const __gri
 
     const uint32_t srow = tid >> 3, seg = tid & 7u; // softmax: 8 threads per row, 4 keys each
     const uint32_t vis = min(it.pos + 1u + (srow >> 3), it.key_hi);
-    const uint32_t klo = max(it.first_pos, it.key_lo);
+    const uint32_t klo = EXT ? lowest_key(it, srow >> 3) : max(it.first_pos, it.key_lo);
     float m_run = NEG_BIG, l_run = 0.0f;
     float *S = reinterpret_cast<float *>(smem + V32_OFF_S);
     float *cfs = reinterpret_cast<float *>(smem + V32_OFF_CF);
@@ -338,15 +339,17 @@ verify_f32_kernel(const VerifyItem *__restrict__ items, int n_items, const __gri
             }
     }
     // the CTAs that finish last merge the pieces (scratch in the ring, which is drained by now)
-    finish_item<256>(it, *reinterpret_cast<FinishSmem *>(smem), status);
+    finish_item<256, EXT>(it, *reinterpret_cast<FinishSmem *>(smem), status);
 }
 
 mkv_status verify_f32_setup_device() {
-    MKV_CUDA(cudaFuncSetAttribute(verify_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)V32_SMEM));
+    MKV_CUDA(cudaFuncSetAttribute(verify_f32_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)V32_SMEM));
+    MKV_CUDA(cudaFuncSetAttribute(verify_f32_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)V32_SMEM));
     return MKV_OK;
 }
 
-mkv_status launch_verify_f32(Ctx *ctx, const VerifyItem *items_dev, int n, const VerifyLaunch &single, uint32_t total_ctas) {
+mkv_status launch_verify_f32(Ctx *ctx, const VerifyItem *items_dev, int n, const VerifyLaunch &single, uint32_t total_ctas,
+                             bool ext) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(total_ctas);
     cfg.blockDim = dim3(256);
@@ -357,7 +360,8 @@ mkv_status launch_verify_f32(Ctx *ctx, const VerifyItem *items_dev, int n, const
     at[0].val.programmaticStreamSerializationAllowed = ctx->pdl ? 1 : 0;
     cfg.attrs = at;
     cfg.numAttrs = 1;
-    MKV_CUDA(cudaLaunchKernelEx(&cfg, verify_f32_kernel, items_dev, n, single, ctx->dev_status));
+    if (ext) MKV_CUDA(cudaLaunchKernelEx(&cfg, verify_f32_kernel<true>, items_dev, n, single, ctx->dev_status));
+    else MKV_CUDA(cudaLaunchKernelEx(&cfg, verify_f32_kernel<false>, items_dev, n, single, ctx->dev_status));
     ctx->launches++;
     return MKV_OK;
 }

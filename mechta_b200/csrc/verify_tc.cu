@@ -115,6 +115,9 @@ __device__ __forceinline__ float vt_transpose_reduce(float (&v)[32], uint32_t la
     return v[0];
 }
 
+// EXT: ring rows, sliding window and sinks (mkv_attn_verify_window, ring caches); the plain path is instantiated
+// without them, which keeps a division and some branches out of the producer's refill path.
+template <bool EXT>
 __global__ void __launch_bounds__(256, 1)
 verify_f16_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __grid_constant__ VerifyLaunch single,
                      uint32_t *__restrict__ status) {
@@ -156,11 +159,14 @@ verify_f16_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
         bool is_v;
         const uint32_t tile = item(n, is_v);
         const CUtensorMap *map = is_v ? vmap : kmap;
-        const int y = (int)(k_begin + tile * VT_TILE - it.row0), x = (int)(kvh * 256u);
+        // the two 64-key boxes of the tile are placed on their own: in a ring cache the second may wrap to row 0
+        const uint32_t key0 = k_begin + tile * VT_TILE;
+        const int y0 = (int)(EXT ? cache_row(it, key0) : key0 - it.row0), y1 = EXT ? (int)cache_row(it, key0 + 64u) : y0 + 64;
+        const int x = (int)(kvh * 256u);
 #pragma unroll
         for (int db = 0; db < 4; db++) {
-            f(map, (uint32_t)db * VT_DB, x + 64 * db, y);
-            f(map, (uint32_t)db * VT_DB + 8192u, x + 64 * db, y + 64);
+            f(map, (uint32_t)db * VT_DB, x + 64 * db, y0);
+            f(map, (uint32_t)db * VT_DB + 8192u, x + 64 * db, y1);
         }
     };
     auto issue = [&](uint32_t n) {
@@ -335,10 +341,13 @@ verify_f16_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
         // ---------------- softmax: one thread per key of the tile (TMEM lane), 32 rows each ----------------
         const uint32_t q4 = warp & 3u, klane = 32u * q4 + lane; // the TMEM lanes this warp may access
         const uint32_t lane_addr = (32u * q4) << 16;
+        // token t of the step sees lowest_key(t) <= key < min(pos + 1 + t, end of the shard, end of this piece)
+        // (M/dmx.rs:71); tiles between the highest lower bound and the lowest upper bound need no mask
         const uint32_t klo = max(it.first_pos, it.key_lo);
-        uint32_t lim[4]; // token t of the step sees keys < lim[t] (M/dmx.rs:71), cut to the shard and to this piece
+        uint32_t lim[4]; // upper bounds per token, cut to the shard and to this piece
 #pragma unroll
         for (uint32_t t = 0; t < 4u; t++) lim[t] = min(min(it.pos + 1u + t, it.key_hi), k_end);
+        const uint32_t lo_max = EXT ? lowest_key(it, 3u) : klo;
         float negm[32], lpart[32]; // minus the row's reference maximum (base-2 units); this key slot's share of the row sums
 #pragma unroll
         for (int r = 0; r < 32; r++) {
@@ -370,10 +379,20 @@ verify_f16_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
                 tmem_ld32(tmem + lane_addr + VT_COL_S + 32u * (j & 1u), sr);
                 tmem_wait_ld();
                 const uint32_t tile_lo = k_begin + j * VT_TILE, key = tile_lo + klane;
-                if (tile_lo < klo || tile_lo + VT_TILE > lim[0]) { // scale, then mask (M/dmx.rs:71)
+                if (tile_lo < lo_max || tile_lo + VT_TILE > lim[0]) { // scale, then mask (M/dmx.rs:71)
+                    if constexpr (EXT) { // the lower bound depends on the token: the window moves with it
 #pragma unroll
-                    for (int r = 0; r < 32; r++)
-                        t[r] = (key >= klo && key < lim[r >> 3]) ? __uint_as_float(sr[r]) * VT_C2 : NEG_BIG;
+                        for (uint32_t tk = 0; tk < 4u; tk++) {
+                            const bool seen = key >= lowest_key(it, tk) && key < lim[tk];
+#pragma unroll
+                            for (int r = 8 * (int)tk; r < 8 * (int)tk + 8; r++)
+                                t[r] = seen ? __uint_as_float(sr[r]) * VT_C2 : NEG_BIG;
+                        }
+                    } else {
+#pragma unroll
+                        for (int r = 0; r < 32; r++)
+                            t[r] = (key >= klo && key < lim[r >> 3]) ? __uint_as_float(sr[r]) * VT_C2 : NEG_BIG;
+                    }
                 } else {
 #pragma unroll
                     for (int r = 0; r < 32; r++) t[r] = __uint_as_float(sr[r]) * VT_C2;
@@ -512,7 +531,7 @@ verify_f16_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
     __syncthreads();
 #endif
     // the CTAs that finish last merge the pieces (scratch in the ring, which is drained by now)
-    finish_item<256>(it, *reinterpret_cast<FinishSmem *>(smem), status);
+    finish_item<256, EXT>(it, *reinterpret_cast<FinishSmem *>(smem), status);
 #ifdef MKV_TRACE
     if (tid == 0) {
         const unsigned int n = atomicAdd(&g_vt_trace_n, 1u);
@@ -544,11 +563,13 @@ extern "C" int mkv_trace_read(unsigned long long *dst, int max_records) {
 #endif
 
 mkv_status verify_tc_setup_device() {
-    MKV_CUDA(cudaFuncSetAttribute(verify_f16_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)VT_SMEM));
+    MKV_CUDA(cudaFuncSetAttribute(verify_f16_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)VT_SMEM));
+    MKV_CUDA(cudaFuncSetAttribute(verify_f16_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)VT_SMEM));
     return MKV_OK;
 }
 
-mkv_status launch_verify_f16_tc(Ctx *ctx, const VerifyItem *items_dev, int n, const VerifyLaunch &single, uint32_t total_ctas) {
+mkv_status launch_verify_f16_tc(Ctx *ctx, const VerifyItem *items_dev, int n, const VerifyLaunch &single, uint32_t total_ctas,
+                                bool ext) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(total_ctas);
     cfg.blockDim = dim3(256);
@@ -559,7 +580,8 @@ mkv_status launch_verify_f16_tc(Ctx *ctx, const VerifyItem *items_dev, int n, co
     at[0].val.programmaticStreamSerializationAllowed = ctx->pdl ? 1 : 0;
     cfg.attrs = at;
     cfg.numAttrs = 1;
-    MKV_CUDA(cudaLaunchKernelEx(&cfg, verify_f16_tc_kernel, items_dev, n, single, ctx->dev_status));
+    if (ext) MKV_CUDA(cudaLaunchKernelEx(&cfg, verify_f16_tc_kernel<true>, items_dev, n, single, ctx->dev_status));
+    else MKV_CUDA(cudaLaunchKernelEx(&cfg, verify_f16_tc_kernel<false>, items_dev, n, single, ctx->dev_status));
     ctx->launches++;
     return MKV_OK;
 }

@@ -137,15 +137,19 @@ class KvCache:
     """The per-layer K and V buffers of the attention layers and the operators that touch them (mkv_cache)."""
 
     def __init__(self, ctx: KvContext, fmt: KvFormat, n_layers: int, context: int, shard_first: int = 0,
-                 shard_tokens: int = 0):
+                 shard_tokens: int = 0, ring: int = 0):
         """context: the sequence's context (check_ctx rule). shard_tokens = 0: the whole context lives here;
-        otherwise only rows [shard_first, shard_first + shard_tokens)."""
+        otherwise only rows [shard_first, shard_first + shard_tokens). ring > 0: a ring cache of that many rows,
+        position p in row p % ring (flint.rs:24-26)."""
         self.ctx, self.fmt, self.n_layers = ctx, KvFormat(fmt), n_layers
-        self.context = context
-        self.capacity, self.shard_first = (shard_tokens or context), shard_first
+        self.context, self.ring = context, ring
+        self.capacity, self.shard_first = (ring or shard_tokens or context), shard_first
         self._h = C.c_void_p()
-        check(_lib.lib().mkv_cache_create(ctx._h, int(fmt), n_layers, context, shard_first, shard_tokens,
-                                          C.byref(self._h)))
+        if ring:
+            check(_lib.lib().mkv_cache_create_ring(ctx._h, int(fmt), n_layers, context, ring, C.byref(self._h)))
+        else:
+            check(_lib.lib().mkv_cache_create(ctx._h, int(fmt), n_layers, context, shard_first, shard_tokens,
+                                              C.byref(self._h)))
 
     # -- bookkeeping
     def __len__(self) -> int:
@@ -185,6 +189,12 @@ class KvCache:
     def attn_verify(self, layer: int, first_pos: int, pos: int, q: torch.Tensor, out: torch.Tensor) -> None:
         """q_dmx + attn_dmx2 + attn_fd_combine (dmx.rs) / attn_fd (+combine): q, out f32 [ntok][16][256]."""
         check(_lib.lib().mkv_attn_verify(self._h, layer, first_pos, pos, q.shape[0], _ptr(q), _ptr(out)))
+
+    def attn_verify_window(self, layer: int, window: int, sinks: torch.Tensor | None, pos: int, q: torch.Tensor,
+                           out: torch.Tensor) -> None:
+        """Verify attention with a sliding window (0 = none) and per-head sinks [16] (None = none), on a ring or an
+        ordinary cache (flint.rs:22-26, flint_attn.wgsl:79-82,243-255)."""
+        check(_lib.lib().mkv_attn_verify_window(self._h, layer, window, _ptr(sinks), pos, q.shape[0], _ptr(q), _ptr(out)))
 
     def attn_step(self, layer: int, first_pos: int, pos: int, qf: torch.Tensor, kb: torch.Tensor, vb: torch.Tensor,
                   q_norm: torch.Tensor, k_norm: torch.Tensor, tab: torch.Tensor, out: torch.Tensor | None = None,

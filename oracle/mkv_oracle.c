@@ -511,3 +511,38 @@ void mko_attn_gate(const float *att, const float *qf, uint32_t ntok, float *out)
         out[i] = att[i] * (1.0f / (1.0f + expf(-v)));
     }
 }
+
+/* ---- ring rows, sliding window, sinks (W/flint_attn.wgsl:79-82 kv4 and lo_di, 243-255 attn_fd_merge) ---------- */
+void mko_attn_window_f64(int fmt, const void *kcache, const void *vcache, uint32_t ring, uint32_t win, const float *sinks,
+                         uint32_t pos, uint32_t ntok, const float *q, double *out) {
+    for (uint32_t tl = 0; tl < ntok; tl++) {
+        const uint32_t n = pos + 1u + tl;
+        const uint32_t lo = (win > 0u && n > win) ? n - win : 0u; /* lo_di */
+#pragma omp parallel for schedule(static)
+        for (int h = 0; h < 16; h++) {
+            const uint32_t kvh = (uint32_t)h / 8u;
+            const float *qr = q + (size_t)tl * 4096u + (size_t)h * 256u;
+            double *sc = (double *)malloc((size_t)(n - lo) * sizeof(double));
+            double mx = sinks ? (double)sinks[h] : -INFINITY;
+            for (uint32_t s = lo; s < n; s++) {
+                const size_t kb = (size_t)(ring ? s % ring : s) * 512u + kvh * 256u;
+                double a = 0.0;
+                for (uint32_t d = 0; d < 256u; d++) a += (double)qr[d] * (double)cache_get(fmt, kcache, kb + d);
+                a *= 1.0 / 16.0;
+                sc[s - lo] = a;
+                if (a > mx) mx = a;
+            }
+            double tot = sinks ? exp((double)sinks[h] - mx) : 0.0, acc[256];
+            memset(acc, 0, sizeof acc);
+            for (uint32_t s = lo; s < n; s++) {
+                const double w = exp(sc[s - lo] - mx);
+                tot += w;
+                const size_t vb = (size_t)(ring ? s % ring : s) * 512u + kvh * 256u;
+                for (uint32_t d = 0; d < 256u; d++) acc[d] += w * (double)cache_get(fmt, vcache, vb + d);
+            }
+            double *o = out + (size_t)tl * 4096u + (size_t)h * 256u;
+            for (uint32_t d = 0; d < 256u; d++) o[d] = acc[d] / tot;
+            free(sc);
+        }
+    }
+}

@@ -50,6 +50,13 @@ void mko_append_k(int fmt, void *kcache, uint32_t pos, uint32_t ntok, const floa
 /* W/kv.wgsl:29-33 and W/ops.wgsl:141-145: V rows, convert and store */
 void mko_append_v(int fmt, void *vcache, uint32_t pos, uint32_t ntok, const float *vb);
 
+/* Cache variants of the reference's second model, on this path's geometry (W/flint_attn.wgsl:1-8,79-82,243-255;
+ * M/flint.rs:22-26): position p in row p % ring (ring = 0: row p), token T sees keys pos + T - win < key <= pos + T
+ * (win = 0: all from 0), sinks[16] = per-head logits that join the maximum and the sum of the softmax and never the
+ * output (NULL: none). Accumulation in f64, as mko_attn_ref_f64. */
+void mko_attn_window_f64(int fmt, const void *kcache, const void *vcache, uint32_t ring, uint32_t win, const float *sinks,
+                         uint32_t pos, uint32_t ntok, const float *q, double *out);
+
 /* The step either side of the KV path (M/quad.rs:113-116,125,131):
  * W/ops.wgsl:27-56 rmsnorm with flag 1 (weight) and scale 1: `rows` rows of n values, row r at x[r*step_x],
  * y[r*n + i] = x * (1 / sqrt(sum(x^2)/n + eps)) * w[i]; the sum of squares in the shader's order (thread t adds

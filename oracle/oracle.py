@@ -58,6 +58,7 @@ def lib() -> C.CDLL:
         L.mko_rmsnorm.argtypes = [vp, u32, u32, u32, vp, C.c_float, vp]
         L.mko_rope2.argtypes = [vp, u32, u32, vp, vp]
         L.mko_attn_gate.argtypes = [vp, vp, u32, vp]
+        L.mko_attn_window_f64.argtypes = [i32, vp, vp, u32, u32, vp, u32, u32, vp, vp]
         L.mko_threads.restype = i32
         _lib = L
     return _lib
@@ -194,6 +195,22 @@ def attn_gate(att: np.ndarray, qf: np.ndarray) -> np.ndarray:
     att = np.ascontiguousarray(att, dtype=np.float32); qf = np.ascontiguousarray(qf, dtype=np.float32)
     out = np.empty_like(att)
     lib().mko_attn_gate(_p(att), _p(qf), att.shape[0], _p(out))
+    return out
+
+
+def append_ring(fmt, kc, vc, ring, pos, k, v, tab):
+    """Rows pos.. of a step into a ring cache: row = position % ring (flint_attn.wgsl:54), one row at a time."""
+    k = np.ascontiguousarray(k, dtype=np.float32); v = np.ascontiguousarray(v, dtype=np.float32)
+    for t in range(k.shape[0]):
+        append(fmt, kc, vc, (pos + t) % ring, k[t:t + 1], v[t:t + 1], None if tab is None else tab[t:t + 1])
+
+
+def attn_window_f64(fmt, kc, vc, ring, win, sinks, pos, q) -> np.ndarray:
+    """Attention with ring rows, a sliding window and per-head sinks, accumulated in f64."""
+    q = np.ascontiguousarray(q, dtype=np.float32)
+    out = np.empty(q.shape, dtype=np.float64)
+    sk = None if sinks is None else np.ascontiguousarray(sinks, dtype=np.float32)
+    lib().mko_attn_window_f64(fmt, _p(kc), _p(vc), ring, win, None if sk is None else _p(sk), pos, q.shape[0], _p(q), _p(out))
     return out
 
 

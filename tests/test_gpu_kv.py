@@ -395,6 +395,94 @@ def test_fused_step_argument_errors(ctx):
     cache.close()
 
 
+# ---------------------------------------------------------------- ring rows, window, sinks ---------------------
+
+WTOL = {kv.KvFormat.F16: 2e-3, kv.KvFormat.F32: 1e-5}
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+@pytest.mark.parametrize("pos,ntok,win,use_sinks", [(2500, 4, 513, True), (900, 1, 513, False), (5000, 3, 1000, True),
+                                                    (600, 4, 0, True), (1023, 4, 513, True)])
+def test_ring_cache_window_and_sinks(ctx, oracle, fmt, pos, ntok, win, use_sinks):
+    """Rows at position % ring, a sliding window per token and per-head sinks, against the oracle's f64 reference;
+    the positions run several times round the ring before the step that is checked."""
+    ring = 1024 if win else 1024
+    if win == 0 and pos + ntok > ring:
+        pytest.skip("without a window the whole history must fit the ring")
+    cache = kv.KvCache(ctx, fmt, 2, 8192, ring=ring)
+    f = int(fmt)
+    kc, vc = oracle.new_cache(f, ring), oracle.new_cache(f, ring)
+    for p in range(0, pos, 256):  # the history, through the library's own writer and the oracle's
+        n = min(256, pos - p)
+        k = synth.normal(91, synth.S_K, p, (n, 2, 256)); v = synth.normal(91, synth.S_V, p, (n, 2, 256))
+        tab = kv.rope_table(p, n)
+        cache.append(1, p, dev(k), dev(v), dev(tab))
+        oracle.append_ring(f, kc, vc, ring, p, k, v, tab)
+    k = synth.normal(92, synth.S_KNEW, 0, (ntok, 2, 256)); v = synth.normal(92, synth.S_VNEW, 0, (ntok, 2, 256))
+    tab = kv.rope_table(pos, ntok)
+    cache.append(1, pos, dev(k), dev(v), dev(tab))
+    oracle.append_ring(f, kc, vc, ring, pos, k, v, tab)
+    gk, gv = host_bits(cache, 1)
+    assert np.array_equal(gk, kc) and np.array_equal(gv, vc)  # every ring row, bit for bit
+    q = synth.normal(92, synth.S_Q, 0, (ntok, 16, 256))
+    sinks = (np.linspace(-2.0, 3.0, 16)).astype(np.float32) if use_sinks else None
+    out = torch.empty(ntok, 16, 256, device="cuda")
+    cache.attn_verify_window(1, win, None if sinks is None else dev(sinks), pos, dev(q), out)
+    ctx.sync()
+    want = oracle.attn_window_f64(f, kc, vc, ring, win, sinks, pos, q)
+    assert oracle.max_rel(out.cpu().numpy(), want) < WTOL[fmt]
+    if use_sinks:  # the sinks must matter: without them the result differs
+        out2 = torch.empty_like(out)
+        cache.attn_verify_window(1, win, None, pos, dev(q), out2)
+        ctx.sync()
+        assert oracle.max_rel(out2.cpu().numpy(), want) > 2 * WTOL[fmt]
+    cache.close()
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+def test_window_and_sinks_on_an_ordinary_cache(ctx, oracle, fmt):
+    """The same options on a contiguous cache; window 0 and no sinks is the plain verify."""
+    pos, ntok = 3000, 4
+    cache = kv.KvCache(ctx, fmt, 1, 4096)
+    kc, vc = fill_both(oracle, cache, 0, pos + ntok, 95)
+    q = synth.normal(95, synth.S_Q, 0, (ntok, 16, 256))
+    sinks = np.linspace(1.0, -1.0, 16).astype(np.float32)
+    out = torch.empty(ntok, 16, 256, device="cuda")
+    for win, sk in ((700, sinks), (0, sinks), (64, None), (1, None)):
+        cache.attn_verify_window(0, win, None if sk is None else dev(sk), pos, dev(q), out)
+        ctx.sync()
+        want = oracle.attn_window_f64(int(fmt), kc, vc, 0, win, sk, pos, q)
+        assert oracle.max_rel(out.cpu().numpy(), want) < WTOL[fmt], (win, sk is None)
+    plain = torch.empty_like(out)
+    cache.attn_verify(0, 0, pos, dev(q), plain)
+    cache.attn_verify_window(0, 0, None, pos, dev(q), out)
+    ctx.sync()
+    assert torch.equal(plain, out)
+    cache.close()
+
+
+def test_ring_cache_limits(ctx):
+    with pytest.raises(kv.MkvError):
+        kv.KvCache(ctx, kv.KvFormat.F16, 1, 8192, ring=1000)  # not a multiple of 128
+    cache = kv.KvCache(ctx, kv.KvFormat.F16, 1, 8192, ring=1024)
+    z = lambda *s: torch.zeros(*s, device="cuda")
+    for p in range(0, 2048, 512):
+        cache.append(0, p, z(512, 2, 256), z(512, 2, 256), None)
+    assert len(cache) == 2048
+    with pytest.raises(kv.MkvError):  # 2048 keys do not fit 1024 rows
+        cache.attn_verify(0, 0, 2044, z(4, 16, 256), z(4, 16, 256))
+    with pytest.raises(kv.MkvError):  # window + step larger than the ring
+        cache.attn_verify_window(0, 1022, None, 2044, z(4, 16, 256), z(4, 16, 256))
+    cache.attn_verify_window(0, 1021, None, 2044, z(4, 16, 256), z(4, 16, 256))
+    with pytest.raises(kv.MkvError):
+        cache.attn_prefill(0, 0, 2044, z(4, 16, 256), z(4, 16, 256))
+    with pytest.raises(kv.MkvError):
+        cache.truncate(2040, scrub=True)
+    cache.truncate(2040)
+    ctx.sync()
+    cache.close()
+
+
 # ---------------------------------------------------------------- shards and batches ----------------------------
 
 @pytest.mark.parametrize("fmt", FMTS)
