@@ -39,12 +39,12 @@ constexpr uint32_t VT_OFF_Q = VT_NSLOT * VT_SLOT;    // [4 dim blocks][32 rows][
 constexpr uint32_t VT_QB = 4096;
 constexpr uint32_t VT_OFF_P = VT_OFF_Q + 16384;      // 2 buffers of [2 key blocks][32 rows][64 keys] f16
 constexpr uint32_t VT_PBUF = 8192;
-constexpr uint32_t VT_OFF_RED = VT_OFF_P + 2 * VT_PBUF;     // [32 rows][4 warps] floats
-constexpr uint32_t VT_OFF_BAR = VT_OFF_RED + 512;
+constexpr uint32_t VT_OFF_RED = VT_OFF_P + 2 * VT_PBUF;     // two buffers of [32 rows][4 warps] floats
+constexpr uint32_t VT_OFF_BAR = VT_OFF_RED + 1024;
 // barriers: full[NSLOT], empty[NSLOT], s_full[2], p_full[2], pv_done[2]
 constexpr uint32_t VT_NBAR = 2 * VT_NSLOT + 6;
 constexpr uint32_t VT_OFF_MISC = VT_OFF_BAR + VT_NBAR * 8;
-constexpr uint32_t VT_SMEM = VT_OFF_MISC + 256 + 1024;
+constexpr uint32_t VT_SMEM = VT_OFF_MISC + 288 + 1024;
 constexpr uint32_t VT_COL_S = 0, VT_COL_O = 64, VT_COLS = 128; // S^T: 2 x 32 columns, O^T: 2 halves x 32
 constexpr long long VT_WAIT_LIMIT = 2000000000ll;
 constexpr float VT_LOG2E = 1.4426950408889634f;
@@ -58,13 +58,14 @@ struct VtShared {
 #ifdef MKV_TRACE
     unsigned long long tr[6];
     unsigned long long tq[8], tp[8], ts[8]; // per tile: QK issued, PV issued, softmax done
+    unsigned long long tu[4];               // first tile: scores loaded, votes done, maxima reduced, references moved
 #endif
 };
 
 #ifdef MKV_TRACE
 // Timeline records for performance work (builds with -DMKV_TRACE only): per CTA
 // [launch, cta, sm, start, after pdl_wait, first K landed, last V landed, piece written, exit, ticket]
-__device__ unsigned long long g_vt_trace[40 * 65536];
+__device__ unsigned long long g_vt_trace[44 * 65536];
 __device__ unsigned int g_vt_trace_n;
 __device__ __forceinline__ unsigned long long vt_now() {
     unsigned long long t;
@@ -354,7 +355,10 @@ verify_f16_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
             negm[r] = VT_UNSET;
             lpart[r] = 0.0f;
         }
-        float *red = reinterpret_cast<float *>(smem + VT_OFF_RED);
+        // two scratch buffers used in turn, so that a reduction's readers never race the next reduction's writers
+        // (between two uses of one buffer lies the barrier of the use of the other)
+        float *red_base = reinterpret_cast<float *>(smem + VT_OFF_RED);
+        uint32_t red_turn = 0;
         // P^T[row][key]: this thread's column, 2 bytes in each of the 32 rows (K-major B operand, 128-byte swizzle)
         uint8_t *pcol = smem + VT_OFF_P + (klane >> 6) * 4096u + (klane & 7u) * 2u;
         const uint32_t kchunk = (klane & 63u) >> 3;
@@ -401,6 +405,9 @@ verify_f16_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
             bool over = false;
 #pragma unroll
             for (int r = 0; r < 32; r++) over |= t[r] + negm[r] > VT_LAZY2;
+#ifdef MKV_TRACE
+            if (tid == 128 && j == 0) sh->tu[0] = vt_now();
+#endif
             // P^T buffer j & 1 belongs to the MMAs of tile j-2 until those have completed
             if (j > 1) ok = __all_sync(0xffffffffu, vt_wait(bar_pv_done + 8u * (j & 1u), ((j >> 1) - 1u) & 1u, sh, status)) && ok;
             tc_fence_after();
@@ -409,31 +416,50 @@ verify_f16_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
                     stopped = true;
                     break;
                 }
-                // move the reference maxima to the true maxima so far: tile maximum of every row over the 128 keys
+#ifdef MKV_TRACE
+                if (tid == 128 && j == 0) sh->tu[1] = vt_now();
+#endif
+                // move the reference maxima to the true maxima so far. The warp's transposing reduction leaves the
+                // maximum of row L over the warp's 32 keys in lane L; after the four warps have met, lane L works
+                // out row L's new reference and rescale factor once and the warp passes them round by shuffles
+                // (every thread keeps all 32: its scores span all rows).
+                float *red = red_base + 128u * (red_turn & 1u);
                 {
                     float mx[32];
 #pragma unroll
                     for (int r = 0; r < 32; r++) mx[r] = t[r];
-                    red[lane * 4u + q4] = vt_transpose_reduce<true>(mx, lane);
+                    red[q4 * 32u + lane] = vt_transpose_reduce<true>(mx, lane);
                 }
                 vt_bar_sync();
+#ifdef MKV_TRACE
+                if (tid == 128 && j == 0) sh->tu[2] = vt_now();
+#endif
+                float my_negm = VT_UNSET, my_cf = 1.0f;
+#pragma unroll
+                for (int r = 0; r < 32; r++)
+                    if (lane == (uint32_t)r) my_negm = negm[r];
+                {
+                    const float mt = fmaxf(fmaxf(red[lane], red[32u + lane]), fmaxf(red[64u + lane], red[96u + lane]));
+                    if (mt > NEG_TEST) {
+                        const bool set = my_negm < 0.5f * VT_UNSET;
+                        const float m_new = set ? fmaxf(-my_negm, mt) : mt;
+                        if (set) my_cf = exp2f(-my_negm - m_new);
+                        my_negm = -m_new;
+                    }
+                }
                 float cf[32];
                 bool any = false;
 #pragma unroll
                 for (int r = 0; r < 32; r++) {
-                    const float4 x = *reinterpret_cast<const float4 *>(red + 4 * r);
-                    const float mt = fmaxf(fmaxf(x.x, x.y), fmaxf(x.z, x.w));
-                    cf[r] = 1.0f;
-                    if (mt > NEG_TEST) {
-                        const bool set = negm[r] < 0.5f * VT_UNSET;
-                        const float m_new = set ? fmaxf(-negm[r], mt) : mt;
-                        if (set) cf[r] = exp2f(-negm[r] - m_new);
-                        negm[r] = -m_new;
-                        lpart[r] *= cf[r];
-                        any |= cf[r] != 1.0f;
-                    }
+                    cf[r] = __shfl_sync(0xffffffffu, my_cf, r);
+                    negm[r] = __shfl_sync(0xffffffffu, my_negm, r);
+                    lpart[r] *= cf[r];
+                    any |= cf[r] != 1.0f;
                 }
-                vt_bar_sync(); // `red` may be written again
+                red_turn++;
+#ifdef MKV_TRACE
+                if (tid == 128 && j == 0) sh->tu[3] = vt_now();
+#endif
                 if (j > 0 && any) {
                     // O^T must hold every tile whose weights used the old references before it is rescaled: the
                     // product of tile j-1 may still be waiting for its V tile
@@ -487,6 +513,7 @@ verify_f16_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
 #pragma unroll
             for (int r = 0; r < 32; r++)
                 if (lane == (uint32_t)r) mrow = negm[r];
+            float *red = red_base + 128u * (red_turn & 1u);
             red[lane * 4u + q4] = vt_transpose_reduce<false>(lpart, lane);
             vt_bar_sync();
             if (q4 == 0) {
@@ -527,6 +554,8 @@ verify_f16_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
     unsigned long long tr[6], tq8[8], tp8[8], ts8[8];
     for (int i = 0; i < 6; i++) tr[i] = sh->tr[i];
     for (int i = 0; i < 8; i++) { tq8[i] = sh->tq[i]; tp8[i] = sh->tp[i]; ts8[i] = sh->ts[i]; }
+    unsigned long long sh_tu[4];
+    for (int i = 0; i < 4; i++) sh_tu[i] = sh->tu[i];
     tr[4] = vt_now();
     __syncthreads();
 #endif
@@ -538,12 +567,13 @@ verify_f16_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
         if (n < 65536u) {
             unsigned int smid;
             asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-            unsigned long long *r = g_vt_trace + 40ull * n;
+            unsigned long long *r = g_vt_trace + 44ull * n;
             r[0] = it.ticket_base; r[1] = blockIdx.x; r[2] = smid; r[3] = tr[0]; r[4] = tr[1]; r[5] = tr[2]; r[6] = tr[3];
             r[7] = tr[4]; r[8] = vt_now(); r[9] = reinterpret_cast<FinishSmem *>(smem)->ticket;
             for (int i = 0; i < 3; i++) r[10 + i] = reinterpret_cast<FinishSmem *>(smem)->tr[i];
             for (int i = 0; i < 8; i++) { r[13 + i] = tq8[i]; r[21 + i] = tp8[i]; r[29 + i] = ts8[i]; }
             r[37] = nt; r[38] = tr[5];
+            for (int i = 0; i < 4; i++) r[40 + i] = sh_tu[i];
         }
     }
 #endif
@@ -555,7 +585,7 @@ extern "C" int mkv_trace_read(unsigned long long *dst, int max_records) {
     cudaMemcpyFromSymbol(&n, g_vt_trace_n, sizeof n);
     if ((int)n > max_records) n = (unsigned int)max_records;
     if (n > 65536u) n = 65536u;
-    cudaMemcpyFromSymbol(dst, g_vt_trace, (size_t)n * 40 * sizeof(unsigned long long));
+    cudaMemcpyFromSymbol(dst, g_vt_trace, (size_t)n * 44 * sizeof(unsigned long long));
     const unsigned int zero = 0;
     cudaMemcpyToSymbol(g_vt_trace_n, &zero, sizeof zero);
     return (int)n;

@@ -17,7 +17,7 @@ import os
 
 import numpy as np
 
-FIELDS = 40  # uint64 per record, see verify_tc.cu
+FIELDS = 44  # uint64 per record, see verify_tc.cu
 
 
 def main() -> None:
@@ -100,6 +100,8 @@ def main() -> None:
                       f"merged max {us(12, m).max():.2f}")
             nt = int(np.bincount(x[:, 37]).argmax())
             full = x[x[:, 37] == nt]
+            print("  first tile: scores seen %.2f | read and scaled %.2f | votes %.2f | maxima reduced %.2f | references moved %.2f | weights start %.2f"
+                  % tuple(np.median(us(c, full)) for c in (20, 40, 41, 42, 43, 28)))
             for name, c0 in (("S^T issued", 13), ("softmax done", 29), ("O^T issued", 21)):
                 print(f"  {name:13s}", " ".join(f"{np.median(us(c0 + j, full)):6.2f}" for j in range(min(nt, 7))))
 

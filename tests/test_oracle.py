@@ -234,3 +234,30 @@ def test_step_operators_around_the_path(oracle):
     g = oracle.attn_gate(att, qf)
     ref = att / (1.0 + np.exp(-qf[:, :, 256:].astype(np.float64)))
     assert np.abs(g - ref).max() < 1e-6
+
+
+@pytest.mark.parametrize("fmt", [0, 1])
+def test_window_reference_reduces_to_the_plain_one(oracle, fmt):
+    """Ring rows, window and sinks of the second model (flint_attn.wgsl:79-82,243-255): with none of them the f64
+    reference is the plain one; a ring only renames rows; the window drops old keys; a sink only scales rows down."""
+    pos, ntok, ring = 300, 3, 256
+    k = synth.normal(31, synth.S_K, 0, (pos + ntok, 2, 256)); v = synth.normal(31, synth.S_V, 0, (pos + ntok, 2, 256))
+    kc, vc = oracle.new_cache(fmt, 512), oracle.new_cache(fmt, 512)
+    oracle.append(fmt, kc, vc, 0, k, v, None)
+    q = synth.normal(31, synth.S_Q, 0, (ntok, 16, 256))
+    plain = oracle.attn_ref_f64(fmt, kc, vc, 0, pos, q)
+    assert np.array_equal(oracle.attn_window_f64(fmt, kc, vc, 0, 0, None, pos, q), plain)
+    # window 100 on the contiguous cache = the same rows placed in a ring of 256 (only the last 256 positions survive)
+    kr, vr = oracle.new_cache(fmt, ring), oracle.new_cache(fmt, ring)
+    oracle.append_ring(fmt, kr, vr, ring, 0, k, v, None)
+    a = oracle.attn_window_f64(fmt, kc, vc, 0, 100, None, pos, q)
+    b = oracle.attn_window_f64(fmt, kr, vr, ring, 100, None, pos, q)
+    assert np.array_equal(a, b) and not np.array_equal(a, plain)
+    # token t with window w = a one-token call whose first position is pos + t + 1 - w
+    for t in range(ntok):
+        one = oracle.attn_ref_f64(fmt, kc, vc, pos + t + 1 - 100, pos + t, q[t:t + 1])
+        assert np.allclose(a[t], one[0], rtol=1e-12, atol=1e-15)
+    # a sink adds exp(sink - max) to every denominator: outputs shrink by a common factor per row
+    s = oracle.attn_window_f64(fmt, kc, vc, 0, 0, np.full(16, 2.0, np.float32), pos, q)
+    ratio = s / plain
+    assert np.all(ratio > 0) and np.all(ratio < 1) and np.allclose(ratio, ratio[..., :1], rtol=1e-9)
