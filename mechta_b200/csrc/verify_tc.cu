@@ -44,7 +44,8 @@ constexpr uint32_t VT_OFF_BAR = VT_OFF_RED + 1024;
 // barriers: full[NSLOT], empty[NSLOT], s_full[2], p_full[2], pv_done[2]
 constexpr uint32_t VT_NBAR = 2 * VT_NSLOT + 6;
 constexpr uint32_t VT_OFF_MISC = VT_OFF_BAR + VT_NBAR * 8;
-constexpr uint32_t VT_SMEM = VT_OFF_MISC + 288 + 1024;
+constexpr uint32_t VT_MISC_BYTES = 512;               // VtShared (a few words; a timeline record in trace builds)
+constexpr uint32_t VT_SMEM = VT_OFF_MISC + VT_MISC_BYTES + 1024;
 constexpr uint32_t VT_COL_S = 0, VT_COL_O = 64, VT_COLS = 128; // S^T: 2 x 32 columns, O^T: 2 halves x 32
 constexpr long long VT_WAIT_LIMIT = 2000000000ll;
 constexpr float VT_LOG2E = 1.4426950408889634f;
@@ -52,30 +53,37 @@ constexpr float VT_C2 = SCALE * VT_LOG2E;            // scores to base-2 exponen
 constexpr float VT_LAZY2 = 8.0f * VT_LOG2E;          // the reference's threshold of 8, in base-2 units
 constexpr float VT_UNSET = 1.0e30f;                  // -(reference maximum) of a row that has seen no key yet
 
-struct VtShared {
-    uint32_t tmem_base;
-    volatile uint32_t abort;
 #ifdef MKV_TRACE
-    unsigned long long tr[6];
-    unsigned long long tq[8], tp[8], ts[8]; // per tile: QK issued, PV issued, softmax done
-    unsigned long long tu[4];               // first tile: scores loaded, votes done, maxima reduced, references moved
-#endif
+// Timeline of one CTA for performance work (builds with -DMKV_TRACE only; read by mechta_b200/trace_timeline.py,
+// which lists the same fields in the same order). All times are %globaltimer nanoseconds.
+struct VtTrace {
+    unsigned long long launch, cta, sm, nt, ticket;               // launch = the item's ticket base, unique per launch
+    unsigned long long start, wait_done, q_ready, piece, exit_;   // CTA start, griddepcontrol.wait returned, Q converted,
+                                                                  // piece written, after the merge
+    unsigned long long fin_ticket, fin_seen, fin_merged;          // merge: ticket taken, all pieces seen, rows merged
+    unsigned long long t0_scores, t0_scaled, t0_votes, t0_reduced, t0_moved, t0_weights; // softmax of the first tile
+    unsigned long long st_issued[8], softmax_done[8], ot_issued[8]; // per tile (the first eight)
 };
-
-#ifdef MKV_TRACE
-// Timeline records for performance work (builds with -DMKV_TRACE only): per CTA
-// [launch, cta, sm, start, after pdl_wait, first K landed, last V landed, piece written, exit, ticket]
-__device__ unsigned long long g_vt_trace[44 * 65536];
+__device__ VtTrace g_vt_trace[65536];
 __device__ unsigned int g_vt_trace_n;
 __device__ __forceinline__ unsigned long long vt_now() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
-#define VT_TRACE(slot) sh->tr[slot] = vt_now()
+#define VT_STAMP(cond, field) do { if (cond) sh->trace.field = vt_now(); } while (0)
 #else
-#define VT_TRACE(slot)
+#define VT_STAMP(cond, field) do { } while (0)
 #endif
+
+struct VtShared {
+    uint32_t tmem_base;
+    volatile uint32_t abort;
+#ifdef MKV_TRACE
+    VtTrace trace;
+#endif
+};
+static_assert(sizeof(VtShared) <= VT_MISC_BYTES, "VtShared outgrew its place in shared memory");
 
 __device__ __forceinline__ bool vt_wait(uint32_t bar, uint32_t parity, VtShared *sh, uint32_t *status) {
     if (sh->abort) return false;
@@ -183,7 +191,7 @@ verify_f16_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
     // starts their loads before that kernel is known to have finished, and before the rest of this prologue.
     uint32_t early = 0;
     if (tid == 0) {
-        VT_TRACE(0);
+        VT_STAMP(true, start);
         for (int s = 0; s < VT_NSLOT; s++) {
             mbar_init(bar_full + 8u * s, 1);
             mbar_init(bar_empty + 8u * s, 1);
@@ -208,7 +216,7 @@ verify_f16_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
     }
     if (warp == 1) tmem_alloc(smem_base + VT_OFF_MISC, VT_COLS); // writes sh->tmem_base
     pdl_wait(); // Q, the newest rows and every global write come after this
-    if (tid == 0) { VT_TRACE(1); }
+    VT_STAMP(tid == 0, wait_done);
 
     // Q of this KV head to shared memory as f16, the B operand of S^T: row = tok * 8 + head % 8 (the order of
     // q_dmx, M/dmx.rs:128-138), rows of tokens >= ntok zero; per 64-dim block [32 rows][128 bytes], 128-byte swizzle
@@ -239,7 +247,7 @@ verify_f16_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = sh->tmem_base;
-    if (tid == 0) { VT_TRACE(5); }
+    VT_STAMP(tid == 0, q_ready);
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -294,10 +302,7 @@ verify_f16_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
                         }
                         tc_commit(bar_empty + 8u * s); // the K tile is free
                         tc_commit(bar_s_full + 8u * (jq & 1u));
-#ifdef MKV_TRACE
-                        if (jq == 0) sh->tr[2] = vt_now();
-                        if (jq < 8) sh->tq[jq] = vt_now();
-#endif
+                        VT_STAMP(jq < 8u, st_issued[jq]);
                         jq++;
                         did = true;
                     }
@@ -319,10 +324,7 @@ verify_f16_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
                             }
                         tc_commit(bar_empty + 8u * s);                 // the V tile is free
                         tc_commit(bar_pv_done + 8u * (jp & 1u));       // O^T holds tiles 0..jp; P^T buffer jp & 1 may be overwritten
-#ifdef MKV_TRACE
-                        if (jp + 1u == nt) sh->tr[3] = vt_now();
-                        if (jp < 8) sh->tp[jp] = vt_now();
-#endif
+                        VT_STAMP(jp < 8u, ot_issued[jp]);
                         jp++;
                         did = true;
                     }
@@ -368,9 +370,7 @@ verify_f16_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
             // a warp takes every wait's outcome together: the TMEM loads are warp-collective
             bool ok = __all_sync(0xffffffffu, vt_wait(bar_s_full + 8u * (j & 1u), (j >> 1) & 1u, sh, status));
             tc_fence_after();
-#ifdef MKV_TRACE
-            if (tid == 128 && j == 0) sh->tq[7] = vt_now();
-#endif
+            VT_STAMP(tid == 128 && j == 0, t0_scores);
             if (ph == 4u) { // measurement: the MMAs without the softmax math, P^T left as it is
                 if (j > 1) __all_sync(0xffffffffu, vt_wait(bar_pv_done + 8u * (j & 1u), ((j >> 1) - 1u) & 1u, sh, status));
                 tc_fence_before();
@@ -405,9 +405,7 @@ verify_f16_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
             bool over = false;
 #pragma unroll
             for (int r = 0; r < 32; r++) over |= t[r] + negm[r] > VT_LAZY2;
-#ifdef MKV_TRACE
-            if (tid == 128 && j == 0) sh->tu[0] = vt_now();
-#endif
+            VT_STAMP(tid == 128 && j == 0, t0_scaled);
             // P^T buffer j & 1 belongs to the MMAs of tile j-2 until those have completed
             if (j > 1) ok = __all_sync(0xffffffffu, vt_wait(bar_pv_done + 8u * (j & 1u), ((j >> 1) - 1u) & 1u, sh, status)) && ok;
             tc_fence_after();
@@ -416,9 +414,7 @@ verify_f16_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
                     stopped = true;
                     break;
                 }
-#ifdef MKV_TRACE
-                if (tid == 128 && j == 0) sh->tu[1] = vt_now();
-#endif
+                VT_STAMP(tid == 128 && j == 0, t0_votes);
                 // move the reference maxima to the true maxima so far. The warp's transposing reduction leaves the
                 // maximum of row L over the warp's 32 keys in lane L; after the four warps have met, lane L works
                 // out row L's new reference and rescale factor once and the warp passes them round by shuffles
@@ -431,9 +427,7 @@ verify_f16_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
                     red[q4 * 32u + lane] = vt_transpose_reduce<true>(mx, lane);
                 }
                 vt_bar_sync();
-#ifdef MKV_TRACE
-                if (tid == 128 && j == 0) sh->tu[2] = vt_now();
-#endif
+                VT_STAMP(tid == 128 && j == 0, t0_reduced);
                 float my_negm = VT_UNSET, my_cf = 1.0f;
 #pragma unroll
                 for (int r = 0; r < 32; r++)
@@ -457,9 +451,7 @@ verify_f16_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
                     any |= cf[r] != 1.0f;
                 }
                 red_turn++;
-#ifdef MKV_TRACE
-                if (tid == 128 && j == 0) sh->tu[3] = vt_now();
-#endif
+                VT_STAMP(tid == 128 && j == 0, t0_moved);
                 if (j > 0 && any) {
                     // O^T must hold every tile whose weights used the old references before it is rescaled: the
                     // product of tile j-1 may still be waiting for its V tile
@@ -483,9 +475,7 @@ verify_f16_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
                     tmem_wait_st();
                 }
             }
-#ifdef MKV_TRACE
-            if (tid == 128 && j == 0) sh->tp[7] = vt_now();
-#endif
+            VT_STAMP(tid == 128 && j == 0, t0_weights);
             // weights: 2^(t - m), rounded to f16 as the reference does (M/dmx.rs:99); the sums run over the rounded values
 #pragma unroll
             for (int r = 0; r < 32; r++) {
@@ -498,9 +488,7 @@ verify_f16_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
             fence_proxy_async();
             tc_fence_before();
             mbar_arrive(bar_p_full + 8u * (j & 1u));
-#ifdef MKV_TRACE
-            if (tid == 128 && j < 8) sh->ts[j] = vt_now();
-#endif
+            VT_STAMP(tid == 128 && j < 8u, softmax_done[j]);
         }
 
         // ---------------- the piece's partial: [m, l] per row and O[32][256] ----------------
@@ -551,12 +539,12 @@ verify_f16_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
         tmem_dealloc(tmem, VT_COLS);
     }
 #ifdef MKV_TRACE
-    unsigned long long tr[6], tq8[8], tp8[8], ts8[8];
-    for (int i = 0; i < 6; i++) tr[i] = sh->tr[i];
-    for (int i = 0; i < 8; i++) { tq8[i] = sh->tq[i]; tp8[i] = sh->tp[i]; ts8[i] = sh->ts[i]; }
-    unsigned long long sh_tu[4];
-    for (int i = 0; i < 4; i++) sh_tu[i] = sh->tu[i];
-    tr[4] = vt_now();
+    // the record leaves shared memory before the merge reuses it
+    VtTrace rec;
+    if (tid == 0) {
+        rec = sh->trace;
+        rec.piece = vt_now();
+    }
     __syncthreads();
 #endif
     // the CTAs that finish last merge the pieces (scratch in the ring, which is drained by now)
@@ -565,27 +553,26 @@ verify_f16_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
     if (tid == 0) {
         const unsigned int n = atomicAdd(&g_vt_trace_n, 1u);
         if (n < 65536u) {
+            const FinishSmem &fs = *reinterpret_cast<const FinishSmem *>(smem);
             unsigned int smid;
             asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-            unsigned long long *r = g_vt_trace + 44ull * n;
-            r[0] = it.ticket_base; r[1] = blockIdx.x; r[2] = smid; r[3] = tr[0]; r[4] = tr[1]; r[5] = tr[2]; r[6] = tr[3];
-            r[7] = tr[4]; r[8] = vt_now(); r[9] = reinterpret_cast<FinishSmem *>(smem)->ticket;
-            for (int i = 0; i < 3; i++) r[10 + i] = reinterpret_cast<FinishSmem *>(smem)->tr[i];
-            for (int i = 0; i < 8; i++) { r[13 + i] = tq8[i]; r[21 + i] = tp8[i]; r[29 + i] = ts8[i]; }
-            r[37] = nt; r[38] = tr[5];
-            for (int i = 0; i < 4; i++) r[40 + i] = sh_tu[i];
+            rec.launch = it.ticket_base; rec.cta = blockIdx.x; rec.sm = smid; rec.nt = nt; rec.ticket = fs.ticket;
+            rec.fin_ticket = fs.tr[0]; rec.fin_seen = fs.tr[1]; rec.fin_merged = fs.tr[2];
+            rec.exit_ = vt_now();
+            g_vt_trace[n] = rec;
         }
     }
 #endif
 }
 
 #ifdef MKV_TRACE
-extern "C" int mkv_trace_read(unsigned long long *dst, int max_records) {
+// Copies the records written so far to `dst` (room for max_records) and starts over. Trace builds only.
+extern "C" int mkv_trace_read(void *dst, int max_records) {
     unsigned int n = 0;
     cudaMemcpyFromSymbol(&n, g_vt_trace_n, sizeof n);
     if ((int)n > max_records) n = (unsigned int)max_records;
     if (n > 65536u) n = 65536u;
-    cudaMemcpyFromSymbol(dst, g_vt_trace, (size_t)n * 44 * sizeof(unsigned long long));
+    cudaMemcpyFromSymbol(dst, g_vt_trace, (size_t)n * sizeof(VtTrace));
     const unsigned int zero = 0;
     cudaMemcpyToSymbol(g_vt_trace_n, &zero, sizeof zero);
     return (int)n;

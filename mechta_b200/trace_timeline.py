@@ -17,7 +17,12 @@ import os
 
 import numpy as np
 
-FIELDS = 44  # uint64 per record, see verify_tc.cu
+# one uint64 per name, in the order of struct VtTrace in csrc/verify_tc.cu
+NAMES = (["launch", "cta", "sm", "nt", "ticket", "start", "wait_done", "q_ready", "piece", "exit", "fin_ticket", "fin_seen",
+          "fin_merged", "t0_scores", "t0_scaled", "t0_votes", "t0_reduced", "t0_moved", "t0_weights"]
+         + [f"st_issued{i}" for i in range(8)] + [f"softmax_done{i}" for i in range(8)] + [f"ot_issued{i}" for i in range(8)])
+COL = {n: i for i, n in enumerate(NAMES)}
+FIELDS = len(NAMES)
 
 
 def main() -> None:
@@ -81,29 +86,31 @@ def main() -> None:
             return
         cnt = lib.mkv_trace_read(buf.ctypes.data_as(C.c_void_p), 65536)
         r = buf[:cnt].astype(np.int64)
-        launches = sorted(set(r[:, 0].tolist()))
+        launches = sorted(set(r[:, COL["launch"]].tolist()))
         prev_t0 = None
         for la in launches[-4:]:
-            x = r[r[:, 0] == la]
-            t0 = x[:, 3].min()
-            us = lambda col, rows=x: (rows[:, col] - t0) / 1e3
+            x = r[r[:, COL["launch"]] == la]
+            t0 = x[:, COL["start"]].min()
+            us = lambda name, rows=x: (rows[:, COL[name]] - t0) / 1e3
+            med = lambda name, rows=x: float(np.median(us(name, rows)))
             period = (t0 - prev_t0) / 1e3 if prev_t0 is not None else float("nan")
             prev_t0 = t0
+            nt = int(np.bincount(x[:, COL["nt"]]).argmax())
+            full = x[x[:, COL["nt"]] == nt]
+            last = f"ot_issued{min(nt, 8) - 1}"
             print(f"launch (ticket base {la}): {len(x)} CTAs, period {period:.2f}")
-            print(f"  start med {np.median(us(3)):.2f} max {us(3).max():.2f} | wait returns med {np.median(us(4)):.2f} | "
-                  f"Q ready med {np.median(us(38)):.2f} | first S^T med {np.median(us(5)):.2f} | "
-                  f"last O^T med {np.median(us(6)):.2f} max {us(6).max():.2f} | last piece {us(7).max():.2f} | "
-                  f"exit med {np.median(us(8)):.2f} max {us(8).max():.2f}")
-            m = x[x[:, 11] > 0]
+            print(f"  start med {med('start'):.2f} max {us('start').max():.2f} | wait returns med {med('wait_done'):.2f} | "
+                  f"Q ready med {med('q_ready'):.2f} | first S^T med {med('st_issued0', full):.2f} | "
+                  f"last O^T med {med(last, full):.2f} max {us(last, full).max():.2f} | last piece {us('piece').max():.2f} | "
+                  f"exit med {med('exit'):.2f} max {us('exit').max():.2f}")
+            m = x[x[:, COL["fin_seen"]] > 0]
             if len(m):
-                print(f"  {len(m)} merging CTAs: ticket med {np.median(us(10, m)):.2f} | all pieces seen med {np.median(us(11, m)):.2f} | "
-                      f"merged max {us(12, m).max():.2f}")
-            nt = int(np.bincount(x[:, 37]).argmax())
-            full = x[x[:, 37] == nt]
-            print("  first tile: scores seen %.2f | read and scaled %.2f | votes %.2f | maxima reduced %.2f | references moved %.2f | weights start %.2f"
-                  % tuple(np.median(us(c, full)) for c in (20, 40, 41, 42, 43, 28)))
-            for name, c0 in (("S^T issued", 13), ("softmax done", 29), ("O^T issued", 21)):
-                print(f"  {name:13s}", " ".join(f"{np.median(us(c0 + j, full)):6.2f}" for j in range(min(nt, 7))))
+                print(f"  {len(m)} merging CTAs: ticket med {med('fin_ticket', m):.2f} | all pieces seen med {med('fin_seen', m):.2f} | "
+                      f"merged max {us('fin_merged', m).max():.2f}")
+            print("  first tile: scores seen %.2f | read and scaled %.2f | votes %.2f | maxima reduced %.2f | references moved %.2f | "
+                  "weights start %.2f" % tuple(med(n, full) for n in ("t0_scores", "t0_scaled", "t0_votes", "t0_reduced", "t0_moved", "t0_weights")))
+            for title, stem in (("S^T issued", "st_issued"), ("softmax done", "softmax_done"), ("O^T issued", "ot_issued")):
+                print(f"  {title:13s}", " ".join(f"{med(stem + str(j), full):6.2f}" for j in range(min(nt, 8))))
 
 
 if __name__ == "__main__":
