@@ -37,8 +37,8 @@ N_LAYERS = 10
 KV_BYTES_F16, KV_BYTES_F32 = 2048, 4096  # K + V bytes per position per layer
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the verify kernel at the decode65k shape, from the
-# ncu capture summarised in profiles/verify_f16_tc_kernel_decode65k.md (139.4..140.2 MB read + 3.1..3.3 MB written)
-NCU_TRAFFIC_BYTES_DECODE65K = 143_000_000
+# ncu capture summarised in profiles/verify_f16_tc_kernel_decode65k.md (134.6 MB read + 4.7 MB written)
+NCU_TRAFFIC_BYTES_DECODE65K = 139_300_000
 
 
 def measured_peaks():
