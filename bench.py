@@ -369,23 +369,23 @@ def run_decode(args, workload):
 
         # ---- end to end through the public API from pinned host buffers
         e2e_steps = min(steps, 200)
-        hq = torch.randn(inp.ring, N_LAYERS, 4, 16, 256).pin_memory()
-        hk = torch.randn(inp.ring, N_LAYERS, 4, 2, 256).pin_memory()
-        hv = torch.randn(inp.ring, N_LAYERS, 4, 2, 256).pin_memory()
+        # one pinned staging row per step: q | k | v | rope table, so that a step's inputs travel in one copy
+        nq, nk, nt_ = N_LAYERS * 4 * 16 * 256, N_LAYERS * 4 * 2 * 256, 4 * 64
+        hin = torch.empty(inp.ring, nq + 2 * nk + nt_).pin_memory()
+        hin[:, :nq + 2 * nk].normal_()
         hout = torch.empty(N_LAYERS, 4, 16, 256).pin_memory()
-        dq, dk, dv = torch.empty_like(inp.q[0]), torch.empty_like(inp.k[0]), torch.empty_like(inp.v[0])
-        dtab = torch.empty(4, 64, device=dev)
-        htab = torch.empty(4, 64).pin_memory()
+        din = torch.empty(nq + 2 * nk + nt_, device=dev)
+        dq = din[:nq].view(N_LAYERS, 4, 16, 256)
+        dk = din[nq:nq + nk].view(N_LAYERS, 4, 2, 256)
+        dv = din[nq + nk:nq + 2 * nk].view(N_LAYERS, 4, 2, 256)
+        dtab = din[nq + 2 * nk:].view(4, 64)
         cache.truncate(min(ctx0, len(cache)))
         pos = ctx0
 
         def e2e_step(s, pos):
             r = s % inp.ring
-            htab.copy_(torch.from_numpy(kv.rope_table(pos, 4)))
-            dq.copy_(hq[r], non_blocking=True)
-            dk.copy_(hk[r], non_blocking=True)
-            dv.copy_(hv[r], non_blocking=True)
-            dtab.copy_(htab, non_blocking=True)
+            hin[r, nq + 2 * nk:].copy_(torch.from_numpy(kv.rope_table(pos, 4)).view(-1))
+            din.copy_(hin[r], non_blocking=True)
             cache.append_layers(pos, dk, dv, dtab)
             for l in range(N_LAYERS):
                 attn(l, pos, dq[l], out[l])
@@ -407,7 +407,7 @@ def run_decode(args, workload):
         f1.record(stream)
         barrier_sync(torch, world)
         e2e_ms = max_over_ranks(torch, world, f0.elapsed_time(f1))
-        h2d = hq[0].numel() * 4 + hk[0].numel() * 4 + hv[0].numel() * 4 + htab.numel() * 4
+        h2d = hin[0].numel() * 4
         d2h = hout.numel() * 4
 
         value = total_bytes / (ms * 1e-3) / 1e9
