@@ -1,4 +1,5 @@
-"""Generates tests/golden/config0.npz: known answers for the CPU-runnable configuration (BASELINE.json configs[0]).
+"""Generates tests/golden/config0.npz: known answers for the CPU-runnable configuration (BASELINE.json configs[0]),
+and tests/golden/step.npz: the fused layer step and the ring / window / sinks variant on the same prior cache.
 
 The reference cannot run where this was written (Rust + wgpu/Vulkan; no graphics stack), and it holds no fixture
 for this path, so these vectors come from the CPU oracle (oracle/mkv_oracle.c) — they pin the oracle against
@@ -40,6 +41,30 @@ def build(fmt):
                 prior_k_sha256=np.frombuffer(hashlib.sha256(kc[:PRIOR].tobytes()).digest(), np.uint8))
 
 
+def build_step(fmt):
+    """The layer step of quad.rs:113-125 at position PRIOR over config 0's cache, and a windowed step with sinks on a
+    ring of 1,024 rows holding the same history (window 513 as flint.rs:22)."""
+    eps, ring, win = 1e-6, 1024, 513
+    kc, vc = oracle.new_cache(fmt, PRIOR + 64), oracle.new_cache(fmt, PRIOR + 64)
+    kr, vr = oracle.new_cache(fmt, ring), oracle.new_cache(fmt, ring)
+    for p in range(0, PRIOR, 1024):
+        k, v = synth.normal(SEED, synth.S_K, p, (1024, 2, 256)), synth.normal(SEED, synth.S_V, p, (1024, 2, 256))
+        tab = oracle.rope_tables(p, 1024)
+        oracle.append(fmt, kc, vc, p, k, v, tab)
+        oracle.append_ring(fmt, kr, vr, ring, p, k, v, tab)
+    qf, kb, vb, qw, kw, sinks = synth.step_inputs(SEED, K)
+    tab = oracle.rope_tables(PRIOR, K)
+    qn = oracle.rmsnorm(qf, 16 * K, 256, 512, qw, eps)
+    kn = oracle.rmsnorm(kb, 2 * K, 256, 256, kw, eps)
+    qr = oracle.rope2(qn, 16, tab).reshape(K, 16, 256)
+    oracle.append(fmt, kc, vc, PRIOR, kn.reshape(K, 2, 256), vb.reshape(K, 2, 256), tab)
+    oracle.append_ring(fmt, kr, vr, ring, PRIOR, kn.reshape(K, 2, 256), vb.reshape(K, 2, 256), tab)
+    ag = oracle.attn_gate(oracle.attn_ref_f32(fmt, kc, vc, 0, PRIOR, qr), qf)
+    windowed = oracle.attn_window_f64(fmt, kr, vr, ring, win, sinks, PRIOR, qr)
+    return dict(step_k=kc[PRIOR:PRIOR + K].copy(), step_v=vc[PRIOR:PRIOR + K].copy(), qr=qr, ag=ag, windowed=windowed,
+                ring_k_sha256=np.frombuffer(hashlib.sha256(kr.tobytes()).digest(), np.uint8))
+
+
 def main():
     data = {"rope_4096": oracle.rope_tables(PRIOR, K), "seed": np.array([SEED, PRIOR, K])}
     for fmt, name in ((0, "f16"), (1, "f32")):
@@ -47,6 +72,12 @@ def main():
             data[f"{name}_{key}"] = val
     np.savez_compressed(os.path.join(os.path.dirname(os.path.abspath(__file__)), "config0.npz"), **data)
     print("wrote config0.npz:", {k: v.shape for k, v in data.items()})
+    step = {"seed": np.array([SEED, PRIOR, K])}
+    for fmt, name in ((0, "f16"), (1, "f32")):
+        for key, val in build_step(fmt).items():
+            step[f"{name}_{key}"] = val
+    np.savez_compressed(os.path.join(os.path.dirname(os.path.abspath(__file__)), "step.npz"), **step)
+    print("wrote step.npz:", {k: v.shape for k, v in step.items()})
 
 
 if __name__ == "__main__":

@@ -68,3 +68,68 @@ def test_gpu_matches_golden(oracle, fmt, name):
     assert oracle.max_rel(win.cpu().numpy(), G[f"{name}_window"]) < TOL[fmt]
     cache.close()
     ctx.close()
+
+
+# ---- tests/golden/step.npz: the fused layer step and the ring / window / sinks variant over the same history ----
+S = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "step.npz"))
+RING, WIN, EPS = 1024, 513, 1e-6
+
+
+@pytest.mark.parametrize("fmt,name", [(0, "f16"), (1, "f32")])
+def test_oracle_reproduces_step_golden(oracle, fmt, name):
+    kc, vc = oracle.new_cache(fmt, PRIOR + 64), oracle.new_cache(fmt, PRIOR + 64)
+    kr, vr = oracle.new_cache(fmt, RING), oracle.new_cache(fmt, RING)
+    for p in range(0, PRIOR, 1024):
+        k, v = synth.normal(SEED, synth.S_K, p, (1024, 2, 256)), synth.normal(SEED, synth.S_V, p, (1024, 2, 256))
+        tab = oracle.rope_tables(p, 1024)
+        oracle.append(fmt, kc, vc, p, k, v, tab)
+        oracle.append_ring(fmt, kr, vr, RING, p, k, v, tab)
+    qf, kb, vb, qw, kw, sinks = synth.step_inputs(SEED, K)
+    tab = oracle.rope_tables(PRIOR, K)
+    kn = oracle.rmsnorm(kb, 2 * K, 256, 256, kw, EPS).reshape(K, 2, 256)
+    qr = oracle.rope2(oracle.rmsnorm(qf, 16 * K, 256, 512, qw, EPS), 16, tab).reshape(K, 16, 256)
+    assert np.array_equal(qr, S[f"{name}_qr"])
+    oracle.append(fmt, kc, vc, PRIOR, kn, vb.reshape(K, 2, 256), tab)
+    oracle.append_ring(fmt, kr, vr, RING, PRIOR, kn, vb.reshape(K, 2, 256), tab)
+    assert np.array_equal(kc[PRIOR:PRIOR + K], S[f"{name}_step_k"]) and np.array_equal(vc[PRIOR:PRIOR + K], S[f"{name}_step_v"])
+    assert hashlib.sha256(kr.tobytes()).digest() == S[f"{name}_ring_k_sha256"].tobytes()
+    ag = oracle.attn_gate(oracle.attn_ref_f32(fmt, kc, vc, 0, PRIOR, qr), qf)
+    assert oracle.max_rel(ag, S[f"{name}_ag"]) < 1e-6  # expf of the C library may differ in the last place between hosts
+    assert oracle.max_rel(oracle.attn_window_f64(fmt, kr, vr, RING, WIN, sinks, PRIOR, qr), S[f"{name}_windowed"]) < 1e-12
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fmt,name", [(0, "f16"), (1, "f32")])
+def test_gpu_step_matches_golden(oracle, fmt, name):
+    import torch
+    from mechta_b200 import kv
+    torch.cuda.set_device(0)
+    ctx = kv.KvContext(0, torch.cuda.current_stream())
+    cache = kv.KvCache(ctx, kv.KvFormat(fmt), 1, 8192)
+    ring = kv.KvCache(ctx, kv.KvFormat(fmt), 1, 8192, ring=RING)
+    to = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    for p in range(0, PRIOR, 1024):
+        k, v = to(synth.normal(SEED, synth.S_K, p, (1024, 2, 256))), to(synth.normal(SEED, synth.S_V, p, (1024, 2, 256)))
+        tab = to(kv.rope_table(p, 1024))
+        cache.append(0, p, k, v, tab)
+        ring.append(0, p, k, v, tab)
+    qf, kb, vb, qw, kw, sinks = synth.step_inputs(SEED, K)
+    tab = to(kv.rope_table(PRIOR, K))
+    ag = torch.empty(K, 16, 256, device="cuda")
+    cache.attn_step(0, 0, PRIOR, to(qf), to(kb), to(vb), to(qw), to(kw), tab, ag, None, EPS)
+    # the step's rows into the ring as they are stored (already normalised and rotated: no table)
+    stored_k = S[f"{name}_step_k"] if fmt == 1 else S[f"{name}_step_k"].view(np.float16).astype(np.float32)
+    ring.append(0, PRIOR, to(stored_k), to(vb.reshape(K, 2, 256)), None)
+    win = torch.empty(K, 16, 256, device="cuda")
+    ring.attn_verify_window(0, WIN, to(sinks), PRIOR, to(S[f"{name}_qr"]), win)
+    ctx.sync()
+    view = (lambda t: t.view(torch.int16).cpu().numpy().view(np.uint16)) if fmt == 0 else (lambda t: t.cpu().numpy())
+    gk, gv = cache.buffer_tensors(0)
+    assert np.array_equal(view(gk)[PRIOR:PRIOR + K], S[f"{name}_step_k"]) and np.array_equal(view(gv)[PRIOR:PRIOR + K], S[f"{name}_step_v"])
+    rk, _ = ring.buffer_tensors(0)
+    assert hashlib.sha256(view(rk).tobytes()).digest() == S[f"{name}_ring_k_sha256"].tobytes()
+    assert oracle.max_rel(ag.cpu().numpy(), S[f"{name}_ag"]) < TOL[fmt]
+    assert oracle.max_rel(win.cpu().numpy(), S[f"{name}_windowed"]) < TOL[fmt]
+    cache.close()
+    ring.close()
+    ctx.close()
