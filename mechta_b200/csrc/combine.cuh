@@ -32,6 +32,7 @@ struct FinishSmem {
     uint32_t ticket, ok;
 #ifdef MKV_TRACE
     unsigned long long tr[3]; // ticket taken, all pieces seen, rows merged
+    unsigned long long tm[4]; // inside the merge of a row: loads issued, maximum known, pieces summed, row written
 #endif
     float4 part[FIN_MAX_THREADS / 64][64];
 };
@@ -67,6 +68,9 @@ __device__ __forceinline__ void merge_row(const VerifyItem &it, uint32_t r, Fini
         const uint32_t s = grp + GROUPS * i;
         x[i] = s < ns ? __ldcg(po + (size_t)s * 2048u) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
+#ifdef MKV_TRACE
+    if (tid == 0) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(sm.tm[0]));
+#endif
     float m = NEG_BIG, l = 0.0f;
     if (tid < ns) {
         const float2 y = __ldcg(ml + (size_t)tid * 32u);
@@ -89,6 +93,9 @@ __device__ __forceinline__ void merge_row(const VerifyItem &it, uint32_t r, Fini
     }
     __syncthreads();
     M = sm.M;
+#ifdef MKV_TRACE
+    if (tid == 0) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(sm.tm[1]));
+#endif
     const float e = tid < ns ? expf(m - M) : 0.0f;
     if (tid < ns) sm.e_s[tid] = e;
     float t = e * l;
@@ -123,6 +130,9 @@ __device__ __forceinline__ void merge_row(const VerifyItem &it, uint32_t r, Fini
     }
     sm.part[grp][d4] = acc;
     __syncthreads();
+#ifdef MKV_TRACE
+    if (tid == 0) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(sm.tm[2]));
+#endif
     if (tid < 64) {
         float4 a = sm.part[0][tid];
 #pragma unroll

@@ -61,6 +61,7 @@ struct VtTrace {
     unsigned long long start, wait_done, q_ready, piece, exit_;   // CTA start, griddepcontrol.wait returned, Q converted,
                                                                   // piece written, after the merge
     unsigned long long fin_ticket, fin_seen, fin_merged;          // merge: ticket taken, all pieces seen, rows merged
+    unsigned long long fin_loads, fin_max, fin_summed;            // merge of a row: loads issued, maximum known, pieces summed
     unsigned long long t0_scores, t0_scaled, t0_votes, t0_reduced, t0_moved, t0_weights; // softmax of the first tile
     unsigned long long st_issued[8], softmax_done[8], ot_issued[8]; // per tile (the first eight)
 };
@@ -558,6 +559,7 @@ verify_f16_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
             asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
             rec.launch = it.ticket_base; rec.cta = blockIdx.x; rec.sm = smid; rec.nt = nt; rec.ticket = fs.ticket;
             rec.fin_ticket = fs.tr[0]; rec.fin_seen = fs.tr[1]; rec.fin_merged = fs.tr[2];
+            rec.fin_loads = fs.tm[0]; rec.fin_max = fs.tm[1]; rec.fin_summed = fs.tm[2];
             rec.exit_ = vt_now();
             g_vt_trace[n] = rec;
         }

@@ -19,7 +19,7 @@ import numpy as np
 
 # one uint64 per name, in the order of struct VtTrace in csrc/verify_tc.cu
 NAMES = (["launch", "cta", "sm", "nt", "ticket", "start", "wait_done", "q_ready", "piece", "exit", "fin_ticket", "fin_seen",
-          "fin_merged", "t0_scores", "t0_scaled", "t0_votes", "t0_reduced", "t0_moved", "t0_weights"]
+          "fin_merged", "fin_loads", "fin_max", "fin_summed", "t0_scores", "t0_scaled", "t0_votes", "t0_reduced", "t0_moved", "t0_weights"]
          + [f"st_issued{i}" for i in range(8)] + [f"softmax_done{i}" for i in range(8)] + [f"ot_issued{i}" for i in range(8)])
 COL = {n: i for i, n in enumerate(NAMES)}
 FIELDS = len(NAMES)
@@ -106,7 +106,8 @@ def main() -> None:
             m = x[x[:, COL["fin_seen"]] > 0]
             if len(m):
                 print(f"  {len(m)} merging CTAs: ticket med {med('fin_ticket', m):.2f} | all pieces seen med {med('fin_seen', m):.2f} | "
-                      f"merged max {us('fin_merged', m).max():.2f}")
+                      f"loads issued med {med('fin_loads', m):.2f} | maximum known med {med('fin_max', m):.2f} | "
+                      f"pieces summed med {med('fin_summed', m):.2f} | merged med {med('fin_merged', m):.2f} max {us('fin_merged', m).max():.2f}")
             print("  first tile: scores seen %.2f | read and scaled %.2f | votes %.2f | maxima reduced %.2f | references moved %.2f | "
                   "weights start %.2f" % tuple(med(n, full) for n in ("t0_scores", "t0_scaled", "t0_votes", "t0_reduced", "t0_moved", "t0_weights")))
             for title, stem in (("S^T issued", "st_issued"), ("softmax done", "softmax_done"), ("O^T issued", "ot_issued")):
