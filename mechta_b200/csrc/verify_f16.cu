@@ -493,6 +493,9 @@ mkv_status verify_f32_setup_device();
 mkv_status launch_verify_f16_tc(Ctx *ctx, const VerifyItem *items_dev, int n, const VerifyLaunch &single, uint32_t total_ctas,
                                 bool ext);
 mkv_status verify_tc_setup_device();
+mkv_status launch_verify_f32_tc(Ctx *ctx, const VerifyItem *items_dev, int n, const VerifyLaunch &single, uint32_t total_ctas,
+                                bool ext);
+mkv_status verify_f32_tc_setup_device();
 
 // MKV_VERIFY=mma selects the warp-MMA kernel of this file for the f16 cache; the default is the tcgen05 kernel.
 static bool verify_use_tc() {
@@ -502,12 +505,21 @@ static bool verify_use_tc() {
     }();
     return tc;
 }
+// MKV_VERIFY32=tc selects the tcgen05 kernel for the f32 cache; the default is the warp-MMA kernel of verify_f32.cu.
+static bool verify32_use_tc() {
+    static const bool tc = [] {
+        const char *e = getenv("MKV_VERIFY32");
+        return e && strcmp(e, "tc") == 0;
+    }();
+    return tc;
+}
 
 // dynamic shared memory opt-in for the current device (once per context creation)
 mkv_status verify_setup_device() {
     MKV_CUDA(cudaFuncSetAttribute(verify_f16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)V16_SMEM));
     mkv_status st = verify_tc_setup_device();
     if (st != MKV_OK) return st;
+    if ((st = verify_f32_tc_setup_device()) != MKV_OK) return st;
     return verify_f32_setup_device();
 }
 
@@ -586,7 +598,8 @@ mkv_status launch_verify(Ctx *ctx, mkv_fmt fmt, VerifyItem *items_host, int n, b
             MKV_CUDA(cudaLaunchKernelEx(&cfg, verify_f16_kernel, items_dev, n, single, ctx->dev_status));
             ctx->launches++;
         } else {
-            mkv_status st = launch_verify_f32(ctx, items_dev, n, single, total, ext);
+            mkv_status st = verify32_use_tc() ? launch_verify_f32_tc(ctx, items_dev, n, single, total, ext)
+                                              : launch_verify_f32(ctx, items_dev, n, single, total, ext);
             if (st != MKV_OK) return st;
         }
         for (int i = 0; i < n; i++) ctx->counter_base[i] += 2u * items_host[i].nsplit;

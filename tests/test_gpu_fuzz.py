@@ -67,3 +67,16 @@ def test_random_steps_against_the_oracle(oracle, seed):
         cache.close()
     assert checked > 20
     ctx.close()
+
+
+def test_f32_cache_on_the_tcgen05_kernel_in_a_child_process():
+    """MKV_VERIFY32=tc selects the tcgen05 kernel for the f32 cache (read once per process, so a child process runs
+    the same random steps with it)."""
+    import os
+    import subprocess
+    import sys
+    env = dict(os.environ, MKV_VERIFY32="tc")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-m", "pytest", os.path.join(root, "tests", "test_gpu_fuzz.py"), "-q", "-x", "-m", "gpu", "-k",
+                        "random_steps"], env=env, cwd=root, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
