@@ -35,11 +35,12 @@ constexpr uint32_t FT_OFF_P = FT_OFF_Q + 32768;       // 2 buffers of P^T hi, lo
 constexpr uint32_t FT_PBUF = 8192;
 constexpr uint32_t FT_OFF_RED = FT_OFF_P + 2 * FT_PBUF;
 constexpr uint32_t FT_OFF_BAR = FT_OFF_RED + 1024;
-// barriers: raw_full[NRAW], raw_empty[NRAW], op_full[NOP], op_empty[NOP], s_full[2], p_full[2], o_full[2], o_free[2]
-constexpr uint32_t FT_NBAR = 2 * FT_NRAW + 2 * FT_NOP + 8;
+// barriers: raw_full[NRAW], raw_empty[NRAW], op_full[NOP], op_empty[NOP], s_full[2], p_full[2], o_full[3], o_free[3]
+constexpr uint32_t FT_NBAR = 2 * FT_NRAW + 2 * FT_NOP + 10;
 constexpr uint32_t FT_OFF_MISC = FT_OFF_BAR + FT_NBAR * 8;
 constexpr uint32_t FT_SMEM = FT_OFF_MISC + 64 + 1024;
-// TMEM columns: S^T main and small x 2 buffers, then per O buffer: main half 0, main half 1, small half 0, small half 1
+// TMEM columns: S^T main and small x 2 buffers, then three O_t buffers (so that folding a tile into the registers is
+// never what the next product waits for), each: main half 0, main half 1, small half 0, small half 1
 constexpr uint32_t FT_COL_S = 0, FT_COL_O = 128, FT_COLS = 512;
 constexpr long long FT_WAIT_LIMIT = 2000000000ll;
 constexpr float FT_LOG2E = 1.4426950408889634f;
@@ -129,7 +130,7 @@ verify_f32_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
     const uint32_t bar0 = smem_base + FT_OFF_BAR;
     const uint32_t bar_raw_full = bar0, bar_raw_empty = bar_raw_full + 8u * FT_NRAW, bar_op_full = bar_raw_empty + 8u * FT_NRAW;
     const uint32_t bar_op_empty = bar_op_full + 8u * FT_NOP, bar_s_full = bar_op_empty + 8u * FT_NOP;
-    const uint32_t bar_p_full = bar_s_full + 16u, bar_o_full = bar_p_full + 16u, bar_o_free = bar_o_full + 16u;
+    const uint32_t bar_p_full = bar_s_full + 16u, bar_o_full = bar_p_full + 16u, bar_o_free = bar_o_full + 24u;
     FtShared *sh = reinterpret_cast<FtShared *>(smem + FT_OFF_MISC);
 
     // The stream of raw sub-tiles: items K0 K1 V0 K2 V1 K3 V2 ... (K one tile ahead of V, so that the softmax of a tile
@@ -174,6 +175,8 @@ verify_f32_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
         for (int i = 0; i < 2; i++) {
             mbar_init(bar_s_full + 8u * i, 1);
             mbar_init(bar_p_full + 8u * i, 128);
+        }
+        for (int i = 0; i < 3; i++) {
             mbar_init(bar_o_full + 8u * i, 1);
             mbar_init(bar_o_free + 8u * i, 128);
         }
@@ -272,7 +275,7 @@ verify_f32_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
                 if (part == 0u && j >= 2u && !(ok = ft_wait(bar_p_full + 8u * (j & 1u), ((j >> 1) - 1u) & 1u, sh, status))) break; // S^T buffer free
                 if (part == 2u) {
                     if (!(ok = ft_wait(bar_p_full + 8u * (j & 1u), (j >> 1) & 1u, sh, status))) break;                         // P^T written
-                    if (j >= 2u && !(ok = ft_wait(bar_o_free + 8u * (j & 1u), ((j >> 1) - 1u) & 1u, sh, status))) break;       // O_t buffer folded
+                    if (j >= 3u && !(ok = ft_wait(bar_o_free + 8u * (j % 3u), ((j / 3u) - 1u) & 1u, sh, status))) break;       // O_t buffer folded
                 }
                 tc_fence_after();
                 if (part < 2u) { // S^T (+)= K_half . Q_half^T : main = hi.hi, small = hi.lo + lo.hi
@@ -292,7 +295,7 @@ verify_f32_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
                     if (half) tc_commit(bar_s_full + 8u * (j & 1u));
                 } else { // O_t^T half = V_half^T . P^T, from zero: main = hi.hi, small = hi.lo + lo.hi
                     const uint32_t pb = smem_base + FT_OFF_P + (j & 1u) * FT_PBUF, pl = pb + 4096u;
-                    const uint32_t d_main = tmem + FT_COL_O + 128u * (j & 1u) + 32u * half, d_small = d_main + 64u;
+                    const uint32_t d_main = tmem + FT_COL_O + 128u * (j % 3u) + 32u * half, d_small = d_main + 64u;
 #pragma unroll
                     for (uint32_t ks = 0; ks < 4u; ks++) { // 16 keys per MMA
                         // V^T, M-major: the next 64 dims one block on, the next 8 keys 1024 bytes on
@@ -305,7 +308,7 @@ verify_f32_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
                         }
                     }
                     tc_commit(bar_op_empty + 8u * ob);
-                    if (half) tc_commit(bar_o_full + 8u * (j & 1u));
+                    if (half) tc_commit(bar_o_full + 8u * (j % 3u));
                 }
             }
         }
@@ -337,9 +340,9 @@ verify_f32_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
 
         // O = O * 1 + O_t of tile jj (main and small accumulators of both halves), then the buffer is free
         auto fold = [&](uint32_t jj) -> bool {
-            bool ok = __all_sync(0xffffffffu, ft_wait(bar_o_full + 8u * (jj & 1u), (jj >> 1) & 1u, sh, status));
+            bool ok = __all_sync(0xffffffffu, ft_wait(bar_o_full + 8u * (jj % 3u), (jj / 3u) & 1u, sh, status));
             tc_fence_after();
-            const uint32_t ob = tmem + lane_addr + FT_COL_O + 128u * (jj & 1u);
+            const uint32_t ob = tmem + lane_addr + FT_COL_O + 128u * (jj % 3u);
 #pragma unroll
             for (uint32_t mh = 0; mh < 2u; mh++) {
                 uint32_t a[32], b[32];
@@ -350,7 +353,7 @@ verify_f32_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
                 for (int r = 0; r < 32; r++) o[mh][r] = __fadd_rn(o[mh][r], __fadd_rn(__uint_as_float(a[r]), __uint_as_float(b[r])));
             }
             tc_fence_before();
-            mbar_arrive(bar_o_free + 8u * (jj & 1u));
+            mbar_arrive(bar_o_free + 8u * (jj % 3u));
             return ok;
         };
 
@@ -377,8 +380,8 @@ verify_f32_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
             bool over = false;
 #pragma unroll
             for (int r = 0; r < 32; r++) over |= t[r] + negm[r] > FT_LAZY2;
-            // P^T buffer j & 1 belongs to the MMAs of tile j-2 until those have completed: they have once tile j-2 is folded
-            while (ok && j >= 2u && folded + 2u <= j) ok = fold(folded++);
+            // P^T buffer j & 1 belongs to the MMAs of tile j-2 until those have completed (its O_t is then full)
+            if (j >= 2u) ok = __all_sync(0xffffffffu, ft_wait(bar_o_full + 8u * ((j - 2u) % 3u), ((j - 2u) / 3u) & 1u, sh, status)) && ok;
             if (ft_bar_or(over || !ok)) {
                 if (ft_bar_or(!ok)) {
                     stopped = true;
@@ -446,6 +449,9 @@ verify_f32_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
             fence_proxy_async();
             tc_fence_before();
             mbar_arrive(bar_p_full + 8u * (j & 1u));
+            // off the critical path: fold the tiles whose products are done (the third O_t buffer gives the slack)
+            bool okf = true;
+            while (okf && j >= 2u && folded + 2u <= j) okf = fold(folded++);
             return true;
         };
 
