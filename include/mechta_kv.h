@@ -105,6 +105,8 @@ uint64_t mkv_cache_device_bytes(const mkv_cache *c);
  * rope_tab_dev = f32 [ntok][64] = [cos 0..31 | sin 0..31] per token (mkv_rope_table), or NULL when K is
  * already rotated. Token t goes to global position pos + t; rows outside this cache's shard are skipped.
  * Afterwards the valid length is pos + ntok (rows beyond it, e.g. refused drafts, are forgotten).
+ * pos may not lie beyond the valid length: rows in between would count as valid without having been written
+ * (MKV_ERR_STATE; a host that fills rows itself declares them with mkv_cache_set_len first).
  * Products and the sum/difference of the rotation are rounded separately (no FMA); f16 stores round to
  * nearest even. 1 <= ntok, pos + ntok <= context. */
 mkv_status mkv_append(mkv_cache *c, int layer, uint32_t pos, uint32_t ntok, const float *k_dev,
@@ -141,16 +143,18 @@ mkv_status mkv_attn_verify_partial(mkv_cache *c, int layer, uint32_t first_pos, 
 mkv_status mkv_combine_shards(mkv_ctx *ctx, const float *recs_dev /*[n_shards][64][258]*/, int n_shards,
                               uint32_t ntok, float *out_dev /*[ntok][16][256]*/);
 
-/* The same exchange without a collective library: each rank's attention kernel stores its record straight into
- * every rank's mailbox over NVLink (plain peer stores, no multicast) and raises a flag; the merge kernel of each rank
- * waits (bounded) for the flags of all ranks. One process per GPU; the mailboxes are shared by CUDA IPC:
+/* The same exchange without a collective library and without a second kernel: the CTAs of the attention kernel that
+ * merge its split-K pieces store each row of the rank's record straight into every rank's mailbox over NVLink (plain
+ * peer stores, no multicast), raise that row's flag there, wait (bounded) for the same row of every other rank in
+ * their own mailbox and write the merged row: one launch per layer. One process per GPU; the mailboxes are shared by
+ * CUDA IPC:
  *   mkv_exchange_create on every rank -> mkv_exchange_handle (64 bytes) -> the host gathers the handles of all ranks
  *   in rank order -> mkv_exchange_connect(handles[world][64]).
  * Every rank then makes the same sequence of mkv_attn_verify_exchange calls (same layer, positions and q): the call
  * number is the epoch that flags carry. out_dev = f32 [ntok][16][256], final (merged over all shards) on every rank.
- * A rank whose handle is all zeroes counts as absent: nothing is sent to it, and since its record never arrives the
- * merge's bounded wait (about two seconds) runs out; the output is then left untouched and mkv_sync reports
- * MKV_ERR_CUDA (status word), after which the context is usable again.
+ * A rank whose handle is all zeroes counts as absent: nothing is sent to it, and since its rows never arrive the
+ * bounded wait of the merging CTAs (about two seconds) runs out; the output is then left untouched and mkv_sync
+ * reports MKV_ERR_CUDA (status word), after which the context is usable again. out_dev must be 16-byte aligned.
  * No counterpart in the reference (one GPU); the arithmetic is attn_fd_combine's (W/ops.wgsl:529-537). */
 typedef struct mkv_exchange mkv_exchange;
 mkv_status mkv_exchange_create(mkv_ctx *ctx, int rank, int world, mkv_exchange **out);
@@ -172,10 +176,19 @@ mkv_status mkv_attn_verify_exchange(mkv_cache *c, mkv_exchange *ex, int layer, u
  * address, opts the kernel into its shared memory and clears the header (a blocking cudaMemset): make that
  * first call before any stream capture begins. All calls share the array, which keeps the previous call's
  * contents (the counter is cleared on the stream before each launch): calls whose kernels may overlap on the
- * GPU, e.g. on two streams, race on it. Calls cudaMalloc / cudaFree nowhere. */
+ * GPU, e.g. on two streams, race on it. Calls cudaMalloc / cudaFree nowhere.
+ * Rows of the caller's buffers past pos + ntok need not be initialised: the kernel reads up to the next multiple
+ * of 64 rows but zeroes the V rows no token sees before it uses the tile, and masked scores are replaced, so a
+ * NaN or infinity left there does not reach the output. The caller's current CUDA device is the same after the
+ * call as before it. The entry point has no context object; it may be called from several host threads (its
+ * once-per-device set-up is guarded by a mutex), but calls that overlap on the GPU still share the one array.
+ * Every wait inside the kernel is bounded; one that runs out sets a status word in the array instead of hanging:
+ * mkv_static_status waits for `stream` (blocks), returns the word in *status_out and clears it; a non-zero word
+ * also makes it return MKV_ERR_CUDA, and the outputs of the calls since the last check are then not valid. */
 mkv_status mkv_attn_verify_static(int device, void *stream, const void *k_dev, const void *v_dev,
                                   uint32_t capacity_tokens, uint32_t first_pos, uint32_t pos, uint32_t ntok,
                                   const float *q_dev, float *out_dev);
+mkv_status mkv_static_status(int device, void *stream, uint32_t *status_out);
 
 /* Ragged batch: n independent (cache, layer, position) verify steps in one launch pair; every cache must
  * belong to `ctx`. Each item behaves exactly as one mkv_attn_verify call. */
@@ -226,9 +239,11 @@ mkv_status mkv_attn_step(mkv_cache *c, int layer, uint32_t first_pos, uint32_t p
 /* ---- prefill attention over the cache: replaces q_f16 + attn_fa_mx + attn_fd_combine (W/fa_mx.wgsl:19-115,
  * 313-319), attn_fa and attn_fd4 (W/ops.wgsl:562-651,711-778), dispatched at M/engine.rs:1215-1241.
  * The block's K/V must already be appended (the reference appends all rows first, M/engine.rs:1213-1214).
- * q_dev f32 [ntok][16][256]; token T sees keys first_pos <= key < pos0 + 1 + T; out f32 [ntok][16][256]. */
+ * q_dev [ntok][16][256]: f32 (`qr`, q_is_f16 = 0) or f16 (`qh`, the output of the reference's q_f16 pass,
+ * q_is_f16 = 1; f16 cache only, as attn_fa_mx); token T sees keys first_pos <= key < pos0 + 1 + T;
+ * out f32 [ntok][16][256]. 1 <= ntok <= 4096. */
 mkv_status mkv_attn_prefill(mkv_cache *c, int layer, uint32_t first_pos, uint32_t pos0, uint32_t ntok,
-                            const float *q_dev, float *out_dev);
+                            const void *q_dev, int q_is_f16, float *out_dev);
 
 /* ---- snapshot / restore of the prefix cache ("root"): replaces the KV part of Engine::read_root /
  * write_root (M/engine.rs:782-823). Payload = for each layer in order, K rows [0,p) then V rows [0,p), raw
@@ -263,7 +278,12 @@ uint64_t mkv_root_key(const uint32_t *tokens, size_t n);
  * (K writers: in0 = kn, in1 = table, u = [256, rows, 0,0, 256,256, flag, pos*512]), "kv_copy", "copy"
  * (V writer: in0 = vb, u = [n, .., extra = pos*512]), "attn_dmx1", "attn_dmx2", "attn_fd", "attn_fd2h"
  * (in0 = qr f32; u as M/quad.rs:286 / M/engine.rs:629; runs the core AND the combine, out = att),
- * "attn_fd_combine", "q_dmx" (no-ops: fused into the attention entry). Anything else: MKV_ERR_UNSUPPORTED. */
+ * "attn_fd_combine", "q_dmx" (no-ops: fused into the attention entry), and the prefill list of
+ * M/engine.rs:1215-1241 with the uniforms of M/engine.rs:915-927: "q_f16" (in0 = qr f32, out = qh f16, u[0] packed
+ * words), "attn_fa_mx" (in0 = qh f16) / "attn_fa" (in0 = qr f32) for the 64 tokens from u[4] = step_a of the block
+ * at position u[0] - 1 (the dispatch of the first split of chunks, u[5] = 0, computes all chunks; later splits
+ * are no-ops), "attn_fd4" (8 tokens from step_a) and "attn_fd" with u[5] = T > 4 (its batch mode); in0 and out are
+ * the whole block's buffers [nb][4096]. Anything else: MKV_ERR_UNSUPPORTED. */
 mkv_status mkv_dispatch(mkv_cache *c, int layer, const char *op, const uint32_t u[8], const void *in0,
                         const void *in1, void *out);
 

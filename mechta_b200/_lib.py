@@ -74,6 +74,7 @@ _SIGS = {
     "mkv_attn_verify_partial": (C.c_int, [C.c_void_p, C.c_int, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p]),
     "mkv_attn_verify_static": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32,
                                          C.c_uint32, C.c_void_p, C.c_void_p]),
+    "mkv_static_status": (C.c_int, [C.c_int, C.c_void_p, C.POINTER(C.c_uint32)]),
     "mkv_exchange_create": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_void_p)]),
     "mkv_exchange_handle": (C.c_int, [C.c_void_p, C.c_void_p]),
     "mkv_exchange_connect": (C.c_int, [C.c_void_p, C.c_void_p]),
@@ -85,7 +86,7 @@ _SIGS = {
     "mkv_cache_create_ring": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_uint32, C.c_uint32, C.POINTER(C.c_void_p)]),
     "mkv_attn_verify_window": (C.c_int, [C.c_void_p, C.c_int, C.c_uint32, C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p]),
     "mkv_attn_step": (C.c_int, [C.c_void_p, C.c_int, C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(StepIn), C.c_void_p, C.c_void_p]),
-    "mkv_attn_prefill": (C.c_int, [C.c_void_p, C.c_int, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p]),
+    "mkv_attn_prefill": (C.c_int, [C.c_void_p, C.c_int, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p, C.c_int, C.c_void_p]),
     "mkv_snapshot_bytes": (C.c_size_t, [C.c_void_p, C.c_uint32]),
     "mkv_snapshot": (C.c_int, [C.c_void_p, C.c_uint32, C.c_void_p, C.c_size_t, C.POINTER(C.c_size_t)]),
     "mkv_snapshot_wait": (C.c_int, [C.c_void_p]),

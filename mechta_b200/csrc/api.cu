@@ -25,7 +25,8 @@ void set_error(const char *fmt, ...) {
 mkv_status prefill_setup_device();
 mkv_status prefill_tc_setup_device();
 mkv_status launch_prefill_f16_tc(Ctx *ctx, Cache *c, int layer, uint32_t first_pos, uint32_t pos0, uint32_t ntok,
-                                 const float *q, float *out);
+                                 const void *q, bool q_is_f16, float *out);
+mkv_status launch_q_f16(Ctx *ctx, const float *src, void *dst, size_t n_pairs);
 mkv_status append_setup_device();
 mkv_status launch_prefill_f16_mma(Ctx *ctx, Cache *c, int layer, uint32_t first_pos, uint32_t pos0, uint32_t ntok,
                                   const float *q, float *out);
@@ -69,14 +70,35 @@ static mkv_status make_tensor_map(CUtensorMap *out, mkv_fmt fmt, void *base, uin
     return MKV_OK;
 }
 
-// MKV_PHASE=1 in the environment: kernels only stream their tiles (to time the loads alone; results are wrong)
+// Measurement builds only (-DMKV_MEASURE): MKV_PHASE in the environment makes the kernels run a part of their work
+// alone (1 = stream the tiles only, ...; results are then wrong). The shipped library ignores the variable.
 static uint32_t measure_phase() {
+#ifdef MKV_MEASURE
     static int v = -1;
     if (v < 0) {
         const char *e = getenv("MKV_PHASE");
         v = e ? atoi(e) : 0;
     }
     return (uint32_t)v;
+#else
+    return 0u;
+#endif
+}
+
+void Cache::note_write(uint32_t pos) {
+    const uint64_t now = ctx->launches;
+    size_t keep = 0;
+    for (size_t i = 0; i < writes.size(); i++)
+        if (writes[i].first + WRITE_WINDOW > now && writes[i].first >= ctx->synced_launches) writes[keep++] = writes[i];
+    writes.resize(keep);
+    writes.push_back({now, pos});
+}
+
+uint32_t Cache::safe_below(uint32_t pos) const {
+    uint32_t lo = pos;
+    for (const auto &w : writes)
+        if (w.first + WRITE_WINDOW > ctx->launches && w.first >= ctx->synced_launches) lo = std::min(lo, w.second);
+    return lo;
 }
 
 static mkv_status use_device(Ctx *ctx) {
@@ -103,14 +125,19 @@ static mkv_status ensure_scratch(Cache *c, size_t pieces) {
     MKV_CUDA(cudaStreamSynchronize(ctx->stream));
     if (c->part_ml) cudaFree(c->part_ml);
     if (c->part_o) cudaFree(c->part_o);
+    if (c->part_flags) cudaFree(c->part_flags);
     c->part_ml = c->part_o = nullptr;
+    c->part_flags = nullptr;
     c->scratch_pieces = 0;
     if (cudaMalloc(&c->part_ml, pieces * 32 * 2 * sizeof(float)) != cudaSuccess ||
-        cudaMalloc(&c->part_o, pieces * 32 * 256 * sizeof(float)) != cudaSuccess) {
+        cudaMalloc(&c->part_o, pieces * 32 * 256 * sizeof(float)) != cudaSuccess ||
+        cudaMalloc(&c->part_flags, pieces * sizeof(uint32_t)) != cudaSuccess) {
         cudaGetLastError();
         set_error("out of device memory for %zu split-K pieces", pieces);
         return MKV_ERR_NOMEM;
     }
+    // a flag holds the number of the launch that wrote its piece; launch numbers start at 1
+    MKV_CUDA(cudaMemsetAsync(c->part_flags, 0, pieces * sizeof(uint32_t), ctx->stream));
     c->scratch_pieces = pieces;
     return MKV_OK;
 }
@@ -176,7 +203,7 @@ static mkv_status fill_item(Cache *c, int layer, uint32_t first_pos, uint32_t po
     it->ring = c->ring;
     it->partial = partial ? 1u : 0u;
     it->phase = measure_phase();
-    it->safe_below = std::min(pos, c->last_write_pos);
+    it->safe_below = c->safe_below(pos);
     if (hi > lo) {
         it->tile_begin = lo / T;
         it->tile_end = (hi + T - 1) / T;
@@ -205,6 +232,7 @@ static mkv_status place_scratch(Cache *const *caches, VerifyItem *items, int n) 
         }
         items[i].part_ml = caches[i]->part_ml + before * 32 * 2;
         items[i].part_o = caches[i]->part_o + before * 32 * 256;
+        items[i].flags = caches[i]->part_flags + before;
     }
     return MKV_OK;
 }
@@ -355,6 +383,7 @@ mkv_status mkv_sync(mkv_ctx *h) {
     if (st != MKV_OK) return st;
     MKV_CUDA(cudaStreamSynchronize(ctx->stream));
     MKV_CUDA(cudaStreamSynchronize(ctx->copy_stream));
+    ctx->synced_launches = ctx->launches;
     return check_device_status(ctx);
 }
 
@@ -535,6 +564,7 @@ void mkv_cache_destroy(mkv_cache *h) {
     if (c->vptrs_dev) cudaFree(c->vptrs_dev);
     if (c->part_ml) cudaFree(c->part_ml);
     if (c->part_o) cudaFree(c->part_o);
+    if (c->part_flags) cudaFree(c->part_flags);
     if (c->qr) cudaFree(c->qr);
     if (c->ev_snapshot) cudaEventDestroy(c->ev_snapshot);
     Ctx *ctx = c->ctx;
@@ -558,12 +588,13 @@ uint32_t mkv_cache_len(const mkv_cache *h) { return h ? reinterpret_cast<const C
 mkv_status mkv_cache_set_len(mkv_cache *h, uint32_t len) {
     Cache *c = reinterpret_cast<Cache *>(h);
     if (!c) return MKV_ERR_INVALID;
-    if (len > c->shard_first + c->capacity) {
-        set_error("length %u beyond the end of the cache %u", len, c->shard_first + c->capacity);
+    const uint32_t end = c->ring ? c->context : c->shard_first + c->capacity; // a ring's rows are reused by later positions
+    if (len > end) {
+        set_error("length %u beyond the end of the cache %u", len, end);
         return MKV_ERR_CAPACITY;
     }
     c->len = len;
-    c->last_write_pos = 0; // the host wrote the buffers itself
+    c->note_write(0); // the host wrote the buffers itself
     return MKV_OK;
 }
 
@@ -588,8 +619,10 @@ void mkv_rope_table(int32_t pos, uint32_t ntok, float *out) {
     }
 }
 
+// which: 1 = the K rows only, 2 = the V rows only, 3 = both. The rows count as valid once their V half is written
+// (the reference dispatches the K writer, then the V writer, M/quad.rs:116-117).
 static mkv_status append_common(Cache *c, int layer0, int n_layers, uint32_t pos, uint32_t ntok, const float *k,
-                                const float *v, const float *tab) {
+                                const float *v, const float *tab, uint32_t which = 3u) {
     if (!c || !k || !v) {
         set_error("null argument");
         return MKV_ERR_INVALID;
@@ -612,14 +645,26 @@ static mkv_status append_common(Cache *c, int layer0, int n_layers, uint32_t pos
         set_error("a ring cache of %u rows cannot take %u rows in one call", c->ring, ntok);
         return MKV_ERR_CAPACITY;
     }
+    {
+        // rows between the valid length and pos that this cache holds would become valid without ever having been written
+        const uint32_t gap_lo = c->ring ? c->len : std::max(c->len, c->shard_first);
+        const uint32_t gap_hi = c->ring ? pos : std::min(pos, shard_end);
+        if (gap_hi > gap_lo) {
+            set_error("rows up to %u are valid, an append at %u would leave a gap (mkv_cache_set_len declares rows the host wrote itself)",
+                      c->len, pos);
+            return MKV_ERR_STATE;
+        }
+    }
     mkv_status st = use_device(c->ctx);
     if (st != MKV_OK) return st;
     st = launch_append(c->ctx, c->fmt, c->kptrs_dev + layer0, c->vptrs_dev + layer0, n_layers, (size_t)ntok * ROW,
-                       c->shard_first, c->capacity, c->ring, pos, ntok, k, v, tab, 3u);
+                       c->shard_first, c->capacity, c->ring, pos, ntok, k, v, tab, which);
     if (st != MKV_OK) return st;
-    c->len = c->ring ? (uint32_t)end : (uint32_t)std::min<uint64_t>(end, shard_end);
-    if (c->len < c->shard_first) c->len = c->shard_first;
-    c->last_write_pos = pos;
+    if (which & 2u) {
+        c->len = c->ring ? (uint32_t)end : (uint32_t)std::min<uint64_t>(end, shard_end);
+        if (c->len < c->shard_first) c->len = c->shard_first;
+    }
+    c->note_write(pos);
     return MKV_OK;
 }
 
@@ -658,7 +703,7 @@ mkv_status mkv_truncate(mkv_cache *h, uint32_t new_len, int scrub) {
     const uint32_t old = c->len;
     c->len = std::max(new_len, std::min(c->shard_first, old));
     if (scrub && old > c->len) {
-        c->last_write_pos = 0;
+        c->note_write(0);
         mkv_status st = use_device(c->ctx);
         if (st != MKV_OK) return st;
         const size_t off = (size_t)(c->len - c->shard_first) * ROW * c->elem;
@@ -714,7 +759,7 @@ mkv_status mkv_attn_step(mkv_cache *h, int layer, uint32_t first_pos, uint32_t p
     }
     // the same checks as an append of these rows followed by a verify over them
     VerifyItem it;
-    const uint32_t len_before = c->len, lw_before = c->last_write_pos;
+    const uint32_t len_before = c->len;
     const uint64_t end = (uint64_t)pos + ntok;
     if (layer < 0 || layer >= c->n_layers || ntok < 1 || ntok > MKV_MAX_VERIFY || end > (uint64_t)c->context) {
         set_error("layer %d, rows [%u, %llu) outside the cache (layers %d, context %u, at most %d rows a step)", layer, pos,
@@ -726,24 +771,29 @@ mkv_status mkv_attn_step(mkv_cache *h, int layer, uint32_t first_pos, uint32_t p
         return MKV_ERR_STATE;
     }
     c->len = (uint32_t)end; // the rows this call writes count as valid for its own attention
-    c->last_write_pos = pos;
+    c->note_write(pos);     // (a note that outlives a failed call only makes later launches more careful)
+    // Everything that can refuse the call comes before the first launch; the length goes back on every failure.
     // fill_item wants an output pointer for its checks; the f16 one serves when there is no f32 output
     mkv_status st = fill_item(c, layer, first_pos, pos, ntok, c->qr, ag ? ag : static_cast<float *>(ag16), false, &it);
+    // a ring cache holds only the last `ring` positions: the keys of the step must fit it (as in mkv_attn_verify)
+    if (st == MKV_OK && c->ring) st = apply_window(c, &it, 0, nullptr);
     if (st == MKV_OK) st = use_device(c->ctx);
-    if (st != MKV_OK) {
-        c->len = len_before;
-        c->last_write_pos = lw_before;
-        return st;
+    Cache *cc[1] = {c};
+    if (st == MKV_OK) {
+        plan_items(c->ctx, &it, 1);
+        st = place_scratch(cc, &it, 1);
     }
     it.out = ag;
     it.gate = in->qf_dev;
     it.out16 = ag16;
-    st = launch_step_prep(c->ctx, c->fmt, in->qf_dev, in->kb_dev, in->vb_dev, in->q_norm_dev, in->k_norm_dev, in->rope_tab_dev,
-                          in->eps, c->qr, c->k[layer], c->v[layer], c->shard_first, c->capacity, c->ring, pos, ntok);
-    if (st != MKV_OK) return st;
-    plan_items(c->ctx, &it, 1);
-    Cache *cc[1] = {c};
-    if ((st = place_scratch(cc, &it, 1)) != MKV_OK) return st;
+    if (st == MKV_OK)
+        st = launch_step_prep(c->ctx, c->fmt, in->qf_dev, in->kb_dev, in->vb_dev, in->q_norm_dev, in->k_norm_dev,
+                              in->rope_tab_dev, in->eps, c->qr, c->k[layer], c->v[layer], c->shard_first, c->capacity, c->ring, pos,
+                              ntok);
+    if (st != MKV_OK) { // nothing was written: the rows of the step are not valid
+        c->len = len_before;
+        return st;
+    }
     return launch_verify(c->ctx, c->fmt, &it, 1, false, &c->maps_host[2 * layer], &c->maps_host[2 * layer + 1]);
 }
 
@@ -780,7 +830,7 @@ mkv_status mkv_exchange_create(mkv_ctx *h, int rank, int world, mkv_exchange **o
     ex->rank = rank;
     ex->world = world;
     ex->flag_off = (2u * (size_t)world * SLOT_FLOATS * sizeof(float) + 255u) & ~(size_t)255u;
-    ex->mailbox_bytes = ex->flag_off + 256;
+    ex->mailbox_bytes = ex->flag_off + 2u * MAX_PEERS * FLAG_WORDS * sizeof(uint32_t);
     if (cudaMalloc(&ex->mailbox, ex->mailbox_bytes) != cudaSuccess || cudaMalloc(&ex->push_dev, sizeof(PushInfo)) != cudaSuccess) {
         cudaGetLastError();
         set_error("out of device memory for the exchange mailbox");
@@ -830,14 +880,16 @@ mkv_status mkv_exchange_connect(mkv_exchange *h, const void *handles) {
     PushInfo pi;
     memset(&pi, 0, sizeof pi);
     pi.world = (uint32_t)ex->world;
-    pi.rows_done = reinterpret_cast<uint32_t *>(ex->mailbox + ex->flag_off + 2 * MAX_PEERS * sizeof(uint32_t));
-    for (int p = 0; p < 2; p++)
+    for (int p = 0; p < 2; p++) {
+        pi.inbox[p] = reinterpret_cast<const float *>(ex->mailbox) + (size_t)p * ex->world * SLOT_FLOATS;
+        pi.inflag[p] = reinterpret_cast<const uint32_t *>(ex->mailbox + ex->flag_off) + (size_t)p * MAX_PEERS * FLAG_WORDS;
         for (int d = 0; d < ex->world; d++) {
             unsigned char *base = static_cast<unsigned char *>(ex->peer_base[d]);
             if (!base) continue;
             pi.slot[p][d] = reinterpret_cast<float *>(base) + ((size_t)p * ex->world + ex->rank) * SLOT_FLOATS;
-            pi.flag[p][d] = reinterpret_cast<uint32_t *>(base + ex->flag_off) + p * MAX_PEERS + ex->rank;
+            pi.rowflag[p][d] = reinterpret_cast<uint32_t *>(base + ex->flag_off) + ((size_t)p * MAX_PEERS + ex->rank) * FLAG_WORDS;
         }
+    }
     MKV_CUDA(cudaMemcpy(ex->push_dev, &pi, sizeof pi, cudaMemcpyHostToDevice));
     ex->connected = true;
     return MKV_OK;
@@ -863,8 +915,12 @@ mkv_status mkv_attn_verify_exchange(mkv_cache *hc, mkv_exchange *hx, int layer, 
         set_error("mkv_attn_verify_exchange: cache and connected exchange of one context needed");
         return MKV_ERR_INVALID;
     }
+    if ((uintptr_t)out & 15u) {
+        set_error("out must be 16-byte aligned");
+        return MKV_ERR_INVALID;
+    }
     VerifyItem it;
-    // the record's destination is the mailboxes; `out` only has to pass the pointer checks here
+    // partial mode: the merged rows are this shard's record; they go to the mailboxes and `out` gets the merge of all ranks
     mkv_status st = fill_item(c, layer, first_pos, pos, ntok, q, out, true, &it);
     if (st != MKV_OK) return st;
     if ((st = use_device(c->ctx)) != MKV_OK) return st;
@@ -875,14 +931,7 @@ mkv_status mkv_attn_verify_exchange(mkv_cache *hc, mkv_exchange *hx, int layer, 
     it.push = ex->push_dev;
     it.push_world = (uint32_t)ex->world;
     it.push_epoch = epoch;
-    it.push_base = ex->rows_base;
-    const uint32_t total = 2u * it.nsplit;
-    if ((st = launch_verify(c->ctx, c->fmt, &it, 1, false, &c->maps_host[2 * layer], &c->maps_host[2 * layer + 1])) != MKV_OK)
-        return st;
-    ex->rows_base += total < 64u ? total : 64u;
-    const float *slots = reinterpret_cast<const float *>(ex->mailbox) + (size_t)(epoch & 1u) * ex->world * SLOT_FLOATS;
-    const uint32_t *flags = reinterpret_cast<const uint32_t *>(ex->mailbox + ex->flag_off) + (epoch & 1u) * MAX_PEERS;
-    return launch_combine_exchange(c->ctx, slots, flags, epoch, ex->world, ntok, out);
+    return launch_verify(c->ctx, c->fmt, &it, 1, false, &c->maps_host[2 * layer], &c->maps_host[2 * layer + 1]);
 }
 
 mkv_status mkv_attn_verify_batch(mkv_ctx *h, const mkv_verify_item *items, int n) {
@@ -918,8 +967,9 @@ mkv_status mkv_attn_verify_batch(mkv_ctx *h, const mkv_verify_item *items, int n
     return launch_verify(ctx, fmt, its.data(), n, true, nullptr, nullptr);
 }
 
-mkv_status mkv_attn_prefill(mkv_cache *h, int layer, uint32_t first_pos, uint32_t pos0, uint32_t ntok, const float *q,
-                            float *out) {
+mkv_status mkv_attn_prefill(mkv_cache *h, int layer, uint32_t first_pos, uint32_t pos0, uint32_t ntok, const void *qv,
+                            int q_is_f16, float *out) {
+    const float *q = static_cast<const float *>(qv);
     Cache *c = reinterpret_cast<Cache *>(h);
     if (!c || !q || !out || layer < 0 || layer >= c->n_layers) {
         set_error("bad argument to mkv_attn_prefill");
@@ -959,8 +1009,16 @@ mkv_status mkv_attn_prefill(mkv_cache *h, int layer, uint32_t first_pos, uint32_
     if (c->fmt == MKV_F16) {
         // MKV_PREFILL=mma selects the warp-MMA kernel (kept as the measured baseline of the tcgen05 kernel)
         static const bool use_mma = [] { const char *e = getenv("MKV_PREFILL"); return e && strcmp(e, "mma") == 0; }();
+        if (use_mma && q_is_f16) {
+            set_error("the warp-MMA baseline kernel (MKV_PREFILL=mma) takes f32 queries only");
+            return MKV_ERR_UNSUPPORTED;
+        }
         return use_mma ? launch_prefill_f16_mma(c->ctx, c, layer, first_pos, pos0, ntok, q, out)
-                       : launch_prefill_f16_tc(c->ctx, c, layer, first_pos, pos0, ntok, q, out);
+                       : launch_prefill_f16_tc(c->ctx, c, layer, first_pos, pos0, ntok, qv, q_is_f16 != 0, out);
+    }
+    if (q_is_f16) {
+        set_error("f16 queries go with the f16 cache (q_f16 + attn_fa_mx); the f32 cache's attn_fa / attn_fd4 read f32 queries");
+        return MKV_ERR_UNSUPPORTED;
     }
     // f32 cache: groups of up to 4 tokens through the f32 verify kernel (the reference's attn_fd4 also reads
     // K/V once per 4 tokens, W/ops.wgsl:694-699), one ragged batch per <= SLOT_ITEMS groups
@@ -1104,7 +1162,7 @@ mkv_status mkv_restore(mkv_cache *h, uint32_t p, const void *src, size_t bytes) 
     MKV_CUDA(cudaEventRecord(ctx->ev_copy, ctx->copy_stream));
     MKV_CUDA(cudaStreamWaitEvent(ctx->stream, ctx->ev_copy, 0));
     c->len = std::max(r1, std::min(c->shard_first, p));
-    c->last_write_pos = 0;
+    c->note_write(0);
     return MKV_OK;
 }
 
@@ -1158,15 +1216,8 @@ mkv_status mkv_dispatch(mkv_cache *h, int layer, const char *op, const uint32_t 
             set_error("%s: missing binding or bad layer", op);
             return MKV_ERR_INVALID;
         }
-        if ((uint64_t)pos + ntok > c->capacity) {
-            set_error("rows [%u, %u) do not fit the cache of %u rows", pos, pos + ntok, c->capacity);
-            return MKV_ERR_CAPACITY;
-        }
-        mkv_status st = use_device(c->ctx);
-        if (st != MKV_OK) return st;
-        return launch_append(c->ctx, c->fmt, c->kptrs_dev + layer, c->vptrs_dev + layer, 1, (size_t)ntok * ROW,
-                             c->shard_first, c->capacity, c->ring, pos, ntok, (const float *)in0, (const float *)in0,
-                             (const float *)in1, 1u);
+        // the K rows only; the rows become valid with the V writer that follows (M/quad.rs:116-117)
+        return append_common(c, layer, 1, pos, ntok, (const float *)in0, (const float *)in0, (const float *)in1, 1u);
     }
     if (is("kv_copy") || is("copy")) {
         const bool compact = op[0] == 'k';
@@ -1183,20 +1234,41 @@ mkv_status mkv_dispatch(mkv_cache *h, int layer, const char *op, const uint32_t 
             set_error("%s: missing binding or bad layer", op);
             return MKV_ERR_INVALID;
         }
-        if ((uint64_t)pos + ntok > c->capacity) {
-            set_error("rows [%u, %u) do not fit the cache of %u rows", pos, pos + ntok, c->capacity);
-            return MKV_ERR_CAPACITY;
+        return append_common(c, layer, 1, pos, ntok, (const float *)in0, (const float *)in0, nullptr, 2u);
+    }
+    if (is("q_dmx") || is("attn_fd_combine")) return MKV_OK; // fused into the attention entry
+    if (is("q_f16")) {
+        // W/fa_mx.wgsl:313-319: n packed words = 2 n values, qr f32 -> qh f16 (the input of attn_fa_mx)
+        if (!in0 || !out || n == 0 || ((uintptr_t)in0 & 15u) || ((uintptr_t)out & 15u) || n % 4u != 0) {
+            set_error("q_f16: in0 = qr (f32), out = qh (f16), both 16-byte aligned, n a multiple of 4 words");
+            return MKV_ERR_INVALID;
         }
         mkv_status st = use_device(c->ctx);
         if (st != MKV_OK) return st;
-        st = launch_append(c->ctx, c->fmt, c->kptrs_dev + layer, c->vptrs_dev + layer, 1, (size_t)ntok * ROW, c->shard_first,
-                           c->capacity, c->ring, pos, ntok, (const float *)in0, (const float *)in0, nullptr, 2u);
-        // the V writer is the second of the pair (M/quad.rs:116-117): the rows are now complete
-        if (st == MKV_OK) c->len = pos + ntok;
-        c->last_write_pos = 0;
-        return st;
+        return launch_q_f16(c->ctx, (const float *)in0, out, n);
     }
-    if (is("q_dmx") || is("attn_fd_combine") || is("q_f16")) return MKV_OK; // fused into the attention entry
+    if (is("attn_fa_mx") || is("attn_fa") || is("attn_fd4") || (is("attn_fd") && step_o > 4u)) {
+        // The prefill forms (uniforms of M/engine.rs:915-927, dispatch list M/engine.rs:1215-1241): tokens
+        // [step_a, step_a + T) of the block that starts at position n - 1, T = 64 for attn_fa_mx / attn_fa (one
+        // dispatch per split of chunks: the call for the first chunk, step_o = 0, does all chunks and the others are
+        // no-ops, as is the attn_fd_combine that follows), 8 for attn_fd4, step_o for attn_fd in its batch mode.
+        // in0 = qh (f16) for attn_fa_mx, qr (f32) otherwise, the whole block's [nb][4096]; out = att [nb][4096].
+        if (fabsf(scale - SCALE) > 0.f) {
+            set_error("%s: scale %g, only 1/16 is built", op, scale);
+            return MKV_ERR_UNSUPPORTED;
+        }
+        const bool fa = is("attn_fa_mx") || is("attn_fa"), mx = is("attn_fa_mx");
+        if (mx && !f16) {
+            set_error("attn_fa_mx runs on the f16 cache only (M/engine.rs:1215)");
+            return MKV_ERR_INVALID;
+        }
+        if (fa && step_o != 0u) return MKV_OK; // a later split of the same group
+        const uint32_t T = fa ? 64u : (is("attn_fd4") ? 8u : step_o);
+        if (n == 0 || !in0 || !out) return MKV_ERR_INVALID;
+        const size_t qoff = (size_t)step_a * 4096u;
+        const void *qg = mx ? (const void *)((const __half *)in0 + qoff) : (const void *)((const float *)in0 + qoff);
+        return mkv_attn_prefill(h, layer, extra, n - 1u + step_a, T, qg, mx ? 1 : 0, (float *)out + qoff);
+    }
     if (is("attn_dmx1") || is("attn_dmx2") || is("attn_fd") || is("attn_fd2h")) {
         if (fabsf(scale - SCALE) > 0.f) {
             set_error("%s: scale %g, only 1/16 is built", op, scale);
@@ -1214,10 +1286,6 @@ mkv_status mkv_dispatch(mkv_cache *h, int layer, const char *op, const uint32_t 
             ntok = 2;
         } else {
             ntok = step_o > 0 ? step_o : 1; // decode: one token per grid z; here one call per token group
-            if (ntok > 4) {
-                set_error("attn_fd in prefill mode (step_o = %u): use mkv_attn_prefill", step_o);
-                return MKV_ERR_UNSUPPORTED;
-            }
         }
         (void)rows;
         (void)step_a;

@@ -90,6 +90,36 @@ append_kernel(void *const *__restrict__ kbufs, void *const *__restrict__ vbufs, 
     }
 }
 
+// q_f16 of the reference (W/fa_mx.wgsl:313-319): the block's rotated queries f32 -> f16, two values per 32-bit word,
+// round to nearest even. One thread = 8 values (two 16-byte loads, one 16-byte store).
+__global__ void __launch_bounds__(256) q_f16_kernel(const float *__restrict__ src, __half *__restrict__ dst, size_t n8) {
+    ptx::pdl_launch_dependents();
+    ptx::pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n8) return;
+    const float4 a = reinterpret_cast<const float4 *>(src)[2 * i], b = reinterpret_cast<const float4 *>(src)[2 * i + 1];
+    const __half2 h0 = __floats2half2_rn(a.x, a.y), h1 = __floats2half2_rn(a.z, a.w);
+    const __half2 h2 = __floats2half2_rn(b.x, b.y), h3 = __floats2half2_rn(b.z, b.w);
+    reinterpret_cast<uint4 *>(dst)[i] = make_uint4(*reinterpret_cast<const uint32_t *>(&h0), *reinterpret_cast<const uint32_t *>(&h1),
+                                                   *reinterpret_cast<const uint32_t *>(&h2), *reinterpret_cast<const uint32_t *>(&h3));
+}
+
+mkv_status launch_q_f16(Ctx *ctx, const float *src, void *dst, size_t n_pairs) {
+    const size_t n8 = n_pairs / 4; // 8 values = 4 packed words per thread
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)((n8 + 255u) / 256u));
+    cfg.blockDim = dim3(256);
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = ctx->pdl ? 1 : 0;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    MKV_CUDA(cudaLaunchKernelEx(&cfg, q_f16_kernel, src, static_cast<__half *>(dst), n8));
+    ctx->launches++;
+    return MKV_OK;
+}
+
 mkv_status append_setup_device() {
     MKV_CUDA(cudaFuncSetAttribute(append_kernel<true>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
     MKV_CUDA(cudaFuncSetAttribute(append_kernel<false>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));

@@ -38,10 +38,13 @@ void set_error(const char *fmt, ...);
 // Peer exchange of shard records without a collective library: where a rank's merged record goes.
 constexpr int MAX_PEERS = 8;
 constexpr size_t SLOT_FLOATS = 64 * 258; // one record [64 rows][258]
+constexpr size_t FLAG_WORDS = 64;        // one flag per record row
 struct PushInfo {
-    float *slot[2][MAX_PEERS];    // [epoch parity][destination rank]: this rank's slot in that rank's mailbox
-    uint32_t *flag[2][MAX_PEERS]; // the word that tells the destination the slot is complete (holds the epoch)
-    uint32_t *rows_done;          // local counter of CTAs that finished pushing, never reset
+    float *slot[2][MAX_PEERS];       // [epoch parity][destination rank]: this rank's record [64][258] in that rank's mailbox
+    uint32_t *rowflag[2][MAX_PEERS]; // [epoch parity][destination rank]: this rank's 64 row flags there (a flag holds the epoch
+                                     // once the row of the record is complete)
+    const float *inbox[2];           // this rank's own mailbox: [epoch parity] -> records [world][64][258]
+    const uint32_t *inflag[2];       // and their row flags [world][64]
     uint32_t world;
 };
 
@@ -65,17 +68,30 @@ struct VerifyItem {
     uint32_t partial;   // 1: write the un-normalised record instead of the final output
     uint32_t *counter;  // arrival counter of this item's CTAs (global memory), never reset
     uint32_t ticket_base; // value of the counter before this launch
-    const PushInfo *push; // partial mode only: push the record to every rank's mailbox instead of `out`
+    uint32_t *flags;    // [2][nsplit] one word per piece: holds `epoch` once the piece of this launch is in global memory;
+                        // null = the pieces are announced by the counter alone (the allocation-free entry point)
+    uint32_t epoch;     // this launch's number on its context (never 0)
+    const PushInfo *push; // partial mode only: the record's rows go to every rank's mailbox, the rows of all ranks are
+                          // merged here and `out` gets the final output
     uint32_t push_world;  // number of ranks (host copy of push->world)
-    uint32_t push_epoch, push_base; // the exchange's call number; value of rows_done before this launch
+    uint32_t push_epoch;  // the exchange's call number
     uint32_t safe_below; // keys below this were not written by the kernel launched just before this one
     uint32_t ring;       // rows of a ring cache (row = position % ring), 0 = rows are positions minus row0
     uint32_t win;        // sliding window: token t sees keys > pos + t - win (0 = no window)
     const float *sinks;  // final mode only: [16] per-head sink logits that join the softmax's max and sum, or null
     const float *gate;   // final mode only: [ntok][16][512] with the output gate in the second half of each head, or null
     void *out16;         // final mode only: the output once more as f16 [ntok][16][256], or null
-    uint32_t phase;     // measurement only, as the reference's p.f1 phases: 0 = everything, 1 = tile loads only
+    uint32_t phase;     // read by builds with -DMKV_MEASURE only (the reference's p.f1 phases: 0 = everything, 1 = tile loads only)
 };
+
+// Measurement builds (make measure: -DMKV_MEASURE) can run parts of a kernel in isolation and record per-CTA
+// timelines; the shipped library compiles all of that out, so its kernels carry no measurement branches.
+#ifdef MKV_MEASURE
+#define MKV_TRACE 1
+#define MKV_PHASE_OF(it) ((it).phase)
+#else
+#define MKV_PHASE_OF(it) 0u
+#endif
 
 // What a single (non-batched) launch carries in the kernel's parameter space: the item and its two tensor
 // maps, so that the TMA unit does not have to fetch the maps from global memory first.
@@ -106,6 +122,8 @@ struct Ctx {
     cudaEvent_t ev_copy = nullptr;    // copy -> compute ordering
     uint32_t *dev_status = nullptr;   // device status word
     uint64_t launches = 0;
+    uint32_t verify_epoch = 0;        // number of the last verify launch (VerifyItem::epoch)
+    uint64_t synced_launches = 0;     // value of `launches` at the last mkv_sync: everything launched before it has finished
     bool pdl = true; // programmatic dependent launch of the attention kernels (MKV_PDL=0 switches it off)
     // profiling of the attention core kernels
     bool prof = false;
@@ -136,7 +154,16 @@ struct Cache {
     uint32_t shard_first = 0;
     bool whole = true;     // holds the whole context (not a sequence shard)
     uint32_t len = 0; // global position after the last valid row
-    uint32_t last_write_pos = 0; // lowest row the most recent writer (append, restore, scrub) touched
+    // Lowest position the recent writers (append, restore, scrub, the host) touched, each with the number of the
+    // context's launch it came before. An attention kernel may load tiles below all of them before the kernels
+    // in front of it have finished: with programmatic dependent launch a whole chain of small launches can be
+    // resident at once, so the writer just in front is not the only one that may still be running. Each
+    // attention CTA fills an SM's shared memory, so at most one per SM can be resident and the chain is shorter
+    // than WRITE_WINDOW launches. Writers launched before the context's last mkv_sync have finished and are dropped.
+    static constexpr uint64_t WRITE_WINDOW = 160;
+    std::vector<std::pair<uint64_t, uint32_t>> writes;
+    void note_write(uint32_t pos);
+    uint32_t safe_below(uint32_t pos) const;
     size_t elem = 2;
     size_t buf_bytes = 0;
     std::vector<void *> k, v;
@@ -147,6 +174,7 @@ struct Cache {
     float *qr = nullptr;             // [4][16][256] normalised and rotated queries of mkv_attn_step (stream-ordered)
     float *part_ml = nullptr;        // split-K scratch, shared by the layers (stream-ordered), grow-only
     float *part_o = nullptr;
+    uint32_t *part_flags = nullptr;  // one word per piece, zeroed when allocated (see VerifyItem::flags)
     size_t scratch_pieces = 0;       // pieces (KV head x split) the scratch holds
     cudaEvent_t ev_snapshot = nullptr;
     bool snapshot_pending = false;
@@ -155,11 +183,11 @@ struct Cache {
 struct Exchange {
     Ctx *ctx = nullptr;
     int rank = 0, world = 1;
-    unsigned char *mailbox = nullptr; // slots[2][world][SLOT_FLOATS] f32, then flags[2][MAX_PEERS] u32, then rows_done
+    unsigned char *mailbox = nullptr; // records[2][world][SLOT_FLOATS] f32, then row flags[2][MAX_PEERS][FLAG_WORDS] u32
     size_t flag_off = 0, mailbox_bytes = 0;
     void *peer_base[MAX_PEERS] = {};
     PushInfo *push_dev = nullptr;
-    uint32_t epoch = 0, rows_base = 0;
+    uint32_t epoch = 0;
     bool connected = false;
 };
 
@@ -173,12 +201,11 @@ mkv_status launch_verify(Ctx *ctx, mkv_fmt fmt, VerifyItem *items_host, int n, b
                          const CUtensorMap *vmap_host);
 mkv_status verify_setup_device();
 mkv_status launch_combine_shards(Ctx *ctx, const float *recs, int n_shards, uint32_t ntok, float *out);
-mkv_status launch_combine_exchange(Ctx *ctx, const float *slots, const uint32_t *flags, uint32_t epoch, int world, uint32_t ntok,
-                                   float *out);
 mkv_status launch_step_prep(Ctx *ctx, mkv_fmt fmt, const float *qf, const float *kb, const float *vb, const float *q_norm,
                             const float *k_norm, const float *tab, float eps, float *qr, void *kcache, void *vcache,
                             uint32_t row_first, uint32_t capacity, uint32_t ring, uint32_t pos, uint32_t ntok);
-mkv_status launch_push_empty(Ctx *ctx, const PushInfo *push, uint32_t epoch, uint32_t world);
+// a shard without any visible key: its (empty) record rows still go to every rank, and the ranks' rows are merged into `out`
+mkv_status launch_exchange_empty(Ctx *ctx, const PushInfo *push, uint32_t epoch, uint32_t ntok, float *out);
 // plans the split of the items so that the grid fills the SMs once
 void plan_items(Ctx *ctx, VerifyItem *items, int n);
 

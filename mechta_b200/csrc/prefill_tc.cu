@@ -52,11 +52,19 @@ __device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, TcShared 
     return false;
 }
 
+// QF16: the queries come as f16 [ntok][16][256] (the output of the reference's q_f16 pass) instead of f32.
+template <bool QF16>
 __global__ void __launch_bounds__(192, 1)
 prefill_f16_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
-                      const float *__restrict__ q, float *__restrict__ out, uint32_t first_pos, uint32_t pos0, uint32_t ntok,
-                      uint32_t row0, uint32_t *__restrict__ status, uint32_t phase) {
-    // phase (measurement only): 0 = everything, 1 = tile loads only, 2 = loads and MMAs without the softmax math
+                      const void *__restrict__ q, float *__restrict__ out, uint32_t first_pos, uint32_t pos0, uint32_t ntok,
+                      uint32_t row0, uint32_t *__restrict__ status, uint32_t phase_arg) {
+    // phase (builds with -DMKV_MEASURE only): 0 = everything, 1 = tile loads only, 2 = loads and MMAs without the softmax math
+#ifdef MKV_MEASURE
+    const uint32_t phase = phase_arg;
+#else
+    constexpr uint32_t phase = 0u;
+    (void)phase_arg;
+#endif
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *smem = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -98,16 +106,30 @@ prefill_f16_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
     if (warp >= 2) {
         const uint32_t row = 32u * (warp & 3u) + lane, lane_addr = (32u * (warp & 3u)) << 16;
         const uint32_t tok = tok0 + (row & 15u), head = 8u * kvh + (row >> 4);
-        const float *src = q + (size_t)min(tok, ntok - 1u) * 4096u + (size_t)head * 256u;
+        const size_t qoff = (size_t)min(tok, ntok - 1u) * 4096u + (size_t)head * 256u;
 #pragma unroll 1
         for (uint32_t c0 = 0; c0 < 4u; c0++) { // 64 dims = 32 columns per store
             uint32_t w[32];
+            if constexpr (QF16) { // already f16: eight 16-byte loads per 64 dims
+                const uint4 *src = reinterpret_cast<const uint4 *>(static_cast<const __half *>(q) + qoff + c0 * 64u);
 #pragma unroll
-            for (int i = 0; i < 16; i++) {
-                const float4 a = *reinterpret_cast<const float4 *>(src + c0 * 64u + 4 * i);
-                const __half2 h0 = __floats2half2_rn(a.x, a.y), h1 = __floats2half2_rn(a.z, a.w);
-                w[2 * i] = tok < ntok ? *reinterpret_cast<const uint32_t *>(&h0) : 0u;
-                w[2 * i + 1] = tok < ntok ? *reinterpret_cast<const uint32_t *>(&h1) : 0u;
+                for (int i = 0; i < 8; i++) {
+                    const uint4 a = src[i];
+                    w[4 * i] = a.x; w[4 * i + 1] = a.y; w[4 * i + 2] = a.z; w[4 * i + 3] = a.w;
+                }
+            } else {
+                const float *src = static_cast<const float *>(q) + qoff + c0 * 64u;
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    const float4 a = *reinterpret_cast<const float4 *>(src + 4 * i);
+                    const __half2 h0 = __floats2half2_rn(a.x, a.y), h1 = __floats2half2_rn(a.z, a.w);
+                    w[2 * i] = *reinterpret_cast<const uint32_t *>(&h0);
+                    w[2 * i + 1] = *reinterpret_cast<const uint32_t *>(&h1);
+                }
+            }
+            if (tok >= ntok) {
+#pragma unroll
+                for (int i = 0; i < 32; i++) w[i] = 0u;
             }
             tmem_st32(tmem + lane_addr + TC_COL_Q + 32u * c0, w);
         }
@@ -296,17 +318,26 @@ prefill_f16_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
 }
 
 mkv_status prefill_tc_setup_device() {
-    MKV_CUDA(cudaFuncSetAttribute(prefill_f16_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM));
+    MKV_CUDA(cudaFuncSetAttribute(prefill_f16_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM));
+    MKV_CUDA(cudaFuncSetAttribute(prefill_f16_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM));
     return MKV_OK;
 }
 
 mkv_status launch_prefill_f16_tc(Ctx *ctx, Cache *c, int layer, uint32_t first_pos, uint32_t pos0, uint32_t ntok,
-                                 const float *q, float *out) {
+                                 const void *q, bool q_is_f16, float *out) {
+#ifdef MKV_MEASURE
     static const uint32_t phase = [] { const char *e = getenv("MKV_PHASE"); return e ? (uint32_t)atoi(e) : 0u; }();
+#else
+    const uint32_t phase = 0u;
+#endif
     const dim3 grid((ntok + 15u) / 16u, 2);
     const CUtensorMap &km = c->maps_host[2 * (c->n_layers + layer)], &vm = c->maps_host[2 * (c->n_layers + layer) + 1];
-    prefill_f16_tc_kernel<<<grid, 192, TC_SMEM, ctx->stream>>>(km, vm, q, out, first_pos, pos0, ntok, c->shard_first,
-                                                               ctx->dev_status, phase);
+    if (q_is_f16)
+        prefill_f16_tc_kernel<true><<<grid, 192, TC_SMEM, ctx->stream>>>(km, vm, q, out, first_pos, pos0, ntok, c->shard_first,
+                                                                         ctx->dev_status, phase);
+    else
+        prefill_f16_tc_kernel<false><<<grid, 192, TC_SMEM, ctx->stream>>>(km, vm, q, out, first_pos, pos0, ntok, c->shard_first,
+                                                                          ctx->dev_status, phase);
     ctx->launches++;
     MKV_CUDA(cudaGetLastError());
     return MKV_OK;

@@ -18,6 +18,8 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <mutex>
+
 #include "combine.cuh"
 #include "internal.cuh"
 #include "ptx.cuh"
@@ -48,12 +50,12 @@ verify_f16_kernel(const VerifyItem *__restrict__ items, int n_items, const __gri
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const uint32_t local = blockIdx.x - it.cta_begin;
     if (local >= 2u * it.nsplit) return;
-    if (it.phase == 2u) return; // measurement: launch cost alone
+    if (MKV_PHASE_OF(it) == 2u) return; // measurement: launch cost alone
     pdl_launch_dependents();    // the next kernel in the stream may begin its own prologue
     const uint32_t kvh = local & 1u, split = local >> 1;
     const uint32_t t0 = it.tile_begin + split * it.tiles_per_split;
     const uint32_t t1 = min(t0 + it.tiles_per_split, it.tile_end);
-    const uint32_t nt = it.phase == 3u ? 0u : t1 - t0; // measurement: prologue and epilogue without tiles
+    const uint32_t nt = MKV_PHASE_OF(it) == 3u ? 0u : t1 - t0; // measurement: prologue and epilogue without tiles
     // a single launch carries its tensor maps in the parameter space
     const CUtensorMap *kmap = items ? it.kmap : &single.kmap, *vmap = items ? it.vmap : &single.vmap;
     const uint32_t bar0 = smem_base + V16_OFF_BAR;
@@ -156,7 +158,22 @@ verify_f16_kernel(const VerifyItem *__restrict__ items, int n_items, const __gri
             atomicOr(status, DEV_ERR_WAIT_TIMEOUT);
         }
         const uint32_t Kb = smem_base + s * V16_STAGE, Vb = Kb + 4 * V16_SUB;
-        if (it.phase == 1u) { // measurement: stream the tiles only
+        {
+            // The tile that holds the last visible key also brings rows past it. Their weights are zero, but zero
+            // times whatever a caller-owned buffer holds there (NaN, infinity) is not: zero those V rows in shared
+            // memory. (K needs nothing: a masked score is replaced, not multiplied.) The stores are ordered before
+            // the P V reads by the two barriers in between.
+            const uint32_t vend = min(it.pos + it.ntok, it.key_hi), tile0 = (t0 + j) * TILE;
+            if (tile0 + TILE > vend) {
+                const uint32_t r0 = vend > tile0 ? vend - tile0 : 0u;
+                uint8_t *vt = smem + (Vb - smem_base);
+                for (uint32_t idx = tid; idx < (TILE - r0) * 32u; idx += 256u) {
+                    const uint32_t row = r0 + (idx >> 5), c = idx & 31u; // 4 dim blocks x 8 chunks of 16 bytes
+                    *reinterpret_cast<uint4 *>(vt + (c >> 3) * V16_SUB + row * 128u + (c & 7u) * 16u) = make_uint4(0, 0, 0, 0);
+                }
+            }
+        }
+        if (MKV_PHASE_OF(it) == 1u) { // measurement: stream the tiles only
             __syncthreads();
             if (tid == 0 && j >= 1 && j - 1 + V16_NST < nt) issue(j - 1 + V16_NST);
             continue;
@@ -406,59 +423,23 @@ combine_shards_kernel(const float *__restrict__ recs, int n_shards, float *__res
     out[(size_t)r * 256u + d] = acc / tot;
 }
 
-// The same merge fed by the peer exchange: slots = this rank's mailbox for the call's parity, [world][64][258],
-// written by the other ranks' attention kernels over NVLink; flags[r] holds the call number once rank r's record is
-// complete. The wait is bounded (a rank that never delivers sets the status word, the output is then left alone).
+// A shard that holds no visible key launches no attention kernel, but it still owes every rank its (empty) record
+// rows, and its own output is the merge of the other ranks' rows: one CTA per row does both (exchange_row).
 __global__ void __launch_bounds__(256)
-combine_exchange_kernel(const float *__restrict__ slots, const uint32_t *__restrict__ flags, uint32_t epoch, int world,
-                        float *__restrict__ out, uint32_t *__restrict__ status) {
-    __shared__ uint32_t ok_s;
-    const uint32_t r = blockIdx.x, d = threadIdx.x;
-    // Launched with programmatic serialization and without griddepcontrol.wait: everything this kernel reads
-    // arrives through the mailbox and is announced by the flags, its own rank's record included, so it may
-    // start (and wait on the flags) while the attention kernel before it is still finishing.
+exchange_empty_kernel(const PushInfo *__restrict__ push, uint32_t epoch, float *__restrict__ out, uint32_t *__restrict__ status) {
+    const uint32_t rr = blockIdx.x, tid = threadIdx.x; // rr = tok * 16 + head
     pdl_launch_dependents();
-    if (d == 0) {
-        const long long t0 = clock64();
-        uint32_t ok = 1;
-        for (int g = 0; g < world && ok; g++)
-            while (ld_acquire_sys(flags + g) != epoch) {
-                __nanosleep(64);
-                if (clock64() - t0 > 4000000000ll) {
-                    ok = 0;
-                    atomicOr(status, DEV_ERR_WAIT_TIMEOUT);
-                    break;
-                }
-            }
-        ok_s = ok;
+    pdl_wait(); // the mailbox parity is free only once the launch before last has finished
+    const PushInfo &P = *push;
+    for (uint32_t dd = 0; dd < P.world; dd++) {
+        float *base = P.slot[epoch & 1u][dd];
+        if (!base) continue; // a rank that never joined the exchange
+        for (uint32_t i = tid; i < (uint32_t)REC; i += 256u) base[(size_t)rr * REC + i] = i == 0 ? NEG_BIG : 0.0f;
     }
-    __syncthreads();
-    if (!ok_s) return;
-    float M = NEG_BIG;
-    for (int g = 0; g < world; g++) M = fmaxf(M, __ldcv(slots + ((size_t)g * 64u + r) * REC));
-    float tot = 0.0f, acc = 0.0f;
-    for (int g = 0; g < world; g++) {
-        const float *x = slots + ((size_t)g * 64u + r) * REC;
-        const float e = expf(__ldcv(x) - M);
-        tot += e * __ldcv(x + 1);
-        acc += e * __ldcv(x + 2 + d);
-    }
-    out[(size_t)r * 256u + d] = acc / tot;
+    exchange_row<256>(P, epoch, rr, out, status);
 }
 
-// A rank whose shard holds no visible key still owes every rank its (empty) record and flag.
-__global__ void __launch_bounds__(256) push_empty_kernel(const PushInfo *__restrict__ push, uint32_t epoch) {
-    const uint32_t dd = blockIdx.x, tid = threadIdx.x;
-    float *slot = push->slot[epoch & 1u][dd];
-    if (!slot) return; // a rank that never joined the exchange
-    for (uint32_t i = tid; i < 64u * REC; i += 256u) slot[i] = (i % REC) == 0 ? NEG_BIG : 0.0f;
-    __threadfence_system();
-    __syncthreads();
-    if (tid == 0) st_release_sys(push->flag[epoch & 1u][dd], epoch);
-}
-
-mkv_status launch_combine_exchange(Ctx *ctx, const float *slots, const uint32_t *flags, uint32_t epoch, int world, uint32_t ntok,
-                                   float *out) {
+mkv_status launch_exchange_empty(Ctx *ctx, const PushInfo *push, uint32_t epoch, uint32_t ntok, float *out) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(16u * ntok);
     cfg.blockDim = dim3(256);
@@ -468,15 +449,8 @@ mkv_status launch_combine_exchange(Ctx *ctx, const float *slots, const uint32_t 
     at[0].val.programmaticStreamSerializationAllowed = ctx->pdl ? 1 : 0;
     cfg.attrs = at;
     cfg.numAttrs = 1;
-    MKV_CUDA(cudaLaunchKernelEx(&cfg, combine_exchange_kernel, slots, flags, epoch, world, out, ctx->dev_status));
+    MKV_CUDA(cudaLaunchKernelEx(&cfg, exchange_empty_kernel, push, epoch, out, ctx->dev_status));
     ctx->launches++;
-    return MKV_OK;
-}
-
-mkv_status launch_push_empty(Ctx *ctx, const PushInfo *push, uint32_t epoch, uint32_t world) {
-    push_empty_kernel<<<world, 256, 0, ctx->stream>>>(push, epoch);
-    ctx->launches++;
-    MKV_CUDA(cudaGetLastError());
     return MKV_OK;
 }
 
@@ -535,7 +509,9 @@ mkv_status launch_verify(Ctx *ctx, mkv_fmt fmt, VerifyItem *items_host, int n, b
     }
     uint32_t total = 0;
     bool any_empty = false, ext = false; // ext: some item uses ring rows, a window or sinks
+    if (++ctx->verify_epoch == 0u) ctx->verify_epoch = 1u; // piece flags hold the launch's number; 0 = never written
     for (int i = 0; i < n; i++) {
+        items_host[i].epoch = ctx->verify_epoch;
         ext |= items_host[i].ring != 0 || items_host[i].win != 0 || items_host[i].sinks != nullptr;
         total += 2u * items_host[i].nsplit;
         any_empty |= items_host[i].nsplit == 0;
@@ -606,7 +582,7 @@ mkv_status launch_verify(Ctx *ctx, mkv_fmt fmt, VerifyItem *items_host, int n, b
     }
     if (ctx->prof) MKV_CUDA(cudaEventRecord(e1, ctx->stream));
     if (any_empty && !batch && items_host[0].push != nullptr) {
-        mkv_status st = launch_push_empty(ctx, items_host[0].push, items_host[0].push_epoch, items_host[0].push_world);
+        mkv_status st = launch_exchange_empty(ctx, items_host[0].push, items_host[0].push_epoch, items_host[0].ntok, items_host[0].out);
         if (st != MKV_OK) return st;
     } else if (any_empty) {
         combine_kernel<<<dim3(64, (unsigned)n), CMB_THREADS, 0, ctx->stream>>>(items_dev, single.item, 1);
@@ -640,6 +616,7 @@ struct StaticDevice {
     int sm_count = 0;
 };
 StaticDevice g_static_dev[STATIC_MAX_DEVICES];
+std::mutex g_static_mutex; // guards g_static_dev and the driver entry point below: the entry point has no context object
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -648,6 +625,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
 // Once per device, with that device current: the device address of the array (in host code its name is only a
 // stand-in, not an address a kernel can use), the shared-memory opt-in of the kernel, the SM count.
 mkv_status static_setup(int device) {
+    std::lock_guard<std::mutex> lock(g_static_mutex);
     StaticDevice &d = g_static_dev[device];
     if (d.ready) return MKV_OK;
     void *p = nullptr;
@@ -684,7 +662,14 @@ extern "C" mkv_status mkv_attn_verify_static(int device, void *stream, const voi
                   capacity_tokens, MKV_CTX_MAX);
         return MKV_ERR_CAPACITY;
     }
-    MKV_CUDA(cudaSetDevice(device));
+    // the caller's current device is put back on every path out of this function
+    struct DeviceGuard {
+        int before = -1;
+        ~DeviceGuard() { if (before >= 0) cudaSetDevice(before); }
+    } guard;
+    MKV_CUDA(cudaGetDevice(&guard.before));
+    if (guard.before == device) guard.before = -1;
+    else MKV_CUDA(cudaSetDevice(device));
     mkv_status st = static_setup(device);
     if (st != MKV_OK) return st;
     const StaticDevice &d = g_static_dev[device];
@@ -718,16 +703,21 @@ extern "C" mkv_status mkv_attn_verify_static(int device, void *stream, const voi
     it.part_ml = reinterpret_cast<float *>(d.scratch + STATIC_HDR);
     it.part_o = reinterpret_cast<float *>(d.scratch + STATIC_HDR + STATIC_ML);
 
-    static EncodeTiledFn enc = nullptr;
-    if (!enc) {
-        void *fn = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess ||
-            q != cudaDriverEntryPointSuccess) {
-            set_error("cuTensorMapEncodeTiled is not available from the driver");
-            return MKV_ERR_CUDA;
+    static EncodeTiledFn enc_fn = nullptr;
+    EncodeTiledFn enc;
+    {
+        std::lock_guard<std::mutex> lock(g_static_mutex);
+        if (!enc_fn) {
+            void *fn = nullptr;
+            cudaDriverEntryPointQueryResult q;
+            if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess ||
+                q != cudaDriverEntryPointSuccess) {
+                set_error("cuTensorMapEncodeTiled is not available from the driver");
+                return MKV_ERR_CUDA;
+            }
+            enc_fn = reinterpret_cast<EncodeTiledFn>(fn);
         }
-        enc = reinterpret_cast<EncodeTiledFn>(fn);
+        enc = enc_fn;
     }
     const cuuint64_t dims[2] = {512, capacity_tokens};
     const cuuint64_t strides[1] = {1024};
@@ -747,6 +737,37 @@ extern "C" mkv_status mkv_attn_verify_static(int device, void *stream, const voi
     MKV_CUDA(cudaMemsetAsync(d.scratch, 0, sizeof(uint32_t), s));
     verify_f16_kernel<<<2u * it.nsplit, 256, V16_SMEM, s>>>(nullptr, 1, L, reinterpret_cast<uint32_t *>(d.scratch + 64));
     MKV_CUDA(cudaGetLastError());
+    return MKV_OK;
+}
+
+extern "C" mkv_status mkv_static_status(int device, void *stream, uint32_t *status_out) {
+    using namespace mkv;
+    if (device < 0 || device >= STATIC_MAX_DEVICES || !status_out) {
+        set_error("mkv_static_status: null pointer or device outside [0, %d)", STATIC_MAX_DEVICES);
+        return MKV_ERR_INVALID;
+    }
+    *status_out = 0;
+    {
+        std::lock_guard<std::mutex> lock(g_static_mutex);
+        if (!g_static_dev[device].ready) return MKV_OK; // nothing ever ran on this device
+    }
+    struct DeviceGuard {
+        int before = -1;
+        ~DeviceGuard() { if (before >= 0) cudaSetDevice(before); }
+    } guard;
+    MKV_CUDA(cudaGetDevice(&guard.before));
+    if (guard.before == device) guard.before = -1;
+    else MKV_CUDA(cudaSetDevice(device));
+    uint32_t *word = reinterpret_cast<uint32_t *>(g_static_dev[device].scratch + 64);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    MKV_CUDA(cudaStreamSynchronize(s));
+    MKV_CUDA(cudaMemcpy(status_out, word, sizeof(uint32_t), cudaMemcpyDeviceToHost));
+    if (*status_out != 0) {
+        MKV_CUDA(cudaMemset(word, 0, sizeof(uint32_t)));
+        set_error("a kernel of mkv_attn_verify_static reported status 0x%x (1 = a bounded wait ran out): its output is not valid",
+                  *status_out);
+        return MKV_ERR_CUDA;
+    }
     return MKV_OK;
 }
 

@@ -117,7 +117,7 @@ verify_f32_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const uint32_t local = blockIdx.x - it.cta_begin;
     if (local >= 2u * it.nsplit) return;
-    const uint32_t ph = it.phase;
+    const uint32_t ph = MKV_PHASE_OF(it);
     if (ph == 2u) return;
     pdl_launch_dependents();
     const uint32_t kvh = local & 1u, split = local >> 1;

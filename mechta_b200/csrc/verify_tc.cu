@@ -54,7 +54,7 @@ constexpr float VT_LAZY2 = 8.0f * VT_LOG2E;          // the reference's threshol
 constexpr float VT_UNSET = 1.0e30f;                  // -(reference maximum) of a row that has seen no key yet
 
 #ifdef MKV_TRACE
-// Timeline of one CTA for performance work (builds with -DMKV_TRACE only; read by mechta_b200/trace_timeline.py,
+// Timeline of one CTA for performance work (builds with -DMKV_MEASURE only; read by mechta_b200/trace_timeline.py,
 // which lists the same fields in the same order). All times are %globaltimer nanoseconds.
 struct VtTrace {
     unsigned long long launch, cta, sm, nt, ticket;               // launch = the item's ticket base, unique per launch
@@ -139,7 +139,7 @@ verify_f16_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const uint32_t local = blockIdx.x - it.cta_begin;
     if (local >= 2u * it.nsplit) return;
-    const uint32_t ph = it.phase;
+    const uint32_t ph = MKV_PHASE_OF(it);
     if (ph == 2u) return; // measurement: launch cost alone
     pdl_launch_dependents();    // the next kernel in the stream may begin its own prologue
     const uint32_t kvh = local & 1u, split = local >> 1;
@@ -223,23 +223,30 @@ verify_f16_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
     // q_dmx, M/dmx.rs:128-138), rows of tokens >= ntok zero; per 64-dim block [32 rows][128 bytes], 128-byte swizzle
     {
         uint8_t *qs = smem + VT_OFF_Q;
+        // All eight loads of a thread go out before the first conversion: written as one loop they would alternate
+        // with the shared-memory stores (the compiler cannot tell the two apart through generic pointers) and the
+        // four round trips to L2 would run one after the other, on the critical path of every launch.
+        float4 qa[4], qb[4];
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             const uint32_t idx = tid + 256u * i; // 32 rows x 32 chunks of 8 dims
-            const uint32_t row = idx >> 5, chunk = idx & 31u;
-            uint4 w = make_uint4(0, 0, 0, 0);
-            const uint32_t tok = row >> 3;
+            const uint32_t row = idx >> 5, chunk = idx & 31u, tok = row >> 3;
+            qa[i] = qb[i] = make_float4(0.f, 0.f, 0.f, 0.f);
             if (tok < it.ntok) {
-                const float *src = it.q + (size_t)tok * 4096u + (size_t)(8u * kvh + (row & 7u)) * 256u + chunk * 8u;
-                const float4 a = *reinterpret_cast<const float4 *>(src);
-                const float4 b = *reinterpret_cast<const float4 *>(src + 4);
-                __half2 h0 = __floats2half2_rn(a.x, a.y), h1 = __floats2half2_rn(a.z, a.w);
-                __half2 h2 = __floats2half2_rn(b.x, b.y), h3 = __floats2half2_rn(b.z, b.w);
-                w.x = *reinterpret_cast<uint32_t *>(&h0);
-                w.y = *reinterpret_cast<uint32_t *>(&h1);
-                w.z = *reinterpret_cast<uint32_t *>(&h2);
-                w.w = *reinterpret_cast<uint32_t *>(&h3);
+                const float4 *src = reinterpret_cast<const float4 *>(it.q + (size_t)tok * 4096u + (size_t)(8u * kvh + (row & 7u)) * 256u +
+                                                                     chunk * 8u);
+                qa[i] = __ldcg(src);
+                qb[i] = __ldcg(src + 1);
             }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const uint32_t idx = tid + 256u * i;
+            const uint32_t row = idx >> 5, chunk = idx & 31u;
+            const __half2 h0 = __floats2half2_rn(qa[i].x, qa[i].y), h1 = __floats2half2_rn(qa[i].z, qa[i].w);
+            const __half2 h2 = __floats2half2_rn(qb[i].x, qb[i].y), h3 = __floats2half2_rn(qb[i].z, qb[i].w);
+            const uint4 w = make_uint4(*reinterpret_cast<const uint32_t *>(&h0), *reinterpret_cast<const uint32_t *>(&h1),
+                                       *reinterpret_cast<const uint32_t *>(&h2), *reinterpret_cast<const uint32_t *>(&h3));
             *reinterpret_cast<uint4 *>(qs + (chunk >> 3) * VT_QB + swz128(row, chunk & 7u)) = w;
         }
     }
@@ -568,7 +575,7 @@ verify_f16_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
 }
 
 #ifdef MKV_TRACE
-// Copies the records written so far to `dst` (room for max_records) and starts over. Trace builds only.
+// Copies the records written so far to `dst` (room for max_records) and starts over. Measurement builds only.
 extern "C" int mkv_trace_read(void *dst, int max_records) {
     unsigned int n = 0;
     cudaMemcpyFromSymbol(&n, g_vt_trace_n, sizeof n);

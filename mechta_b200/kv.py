@@ -211,8 +211,11 @@ class KvCache:
         check(_lib.lib().mkv_attn_verify_partial(self._h, layer, first_pos, pos, q.shape[0], _ptr(q), _ptr(rec)))
 
     def attn_prefill(self, layer: int, first_pos: int, pos0: int, q: torch.Tensor, out: torch.Tensor) -> None:
-        """attn_fa_mx / attn_fa / attn_fd4 (+combine): q, out f32 [ntok][16][256]; K/V appended before."""
-        check(_lib.lib().mkv_attn_prefill(self._h, layer, first_pos, pos0, q.shape[0], _ptr(q), _ptr(out)))
+        """q_f16 + attn_fa_mx / attn_fa / attn_fd4 (+combine): q [ntok][16][256] f32 (`qr`) or f16 (`qh`, f16 cache only),
+        out f32 [ntok][16][256]; the block's K/V appended before."""
+        assert q.dtype in (torch.float32, torch.float16)
+        check(_lib.lib().mkv_attn_prefill(self._h, layer, first_pos, pos0, q.shape[0], _ptr(q), int(q.dtype == torch.float16),
+                                          _ptr(out)))
 
     def dispatch(self, layer: int, op: str, uniform, in0=None, in1=None, out=None) -> None:
         """The reference's own form: WGSL entry point name + its 8-word uniform (ops.wgsl:4)."""

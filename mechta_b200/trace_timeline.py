@@ -1,10 +1,10 @@
 """Timeline of the decode attention kernel inside a chain of launches, and the per-launch time of that chain.
 
-    make -C mechta_b200/csrc trace                         # builds mechta_b200/libmechta_kv_trace.so (-DMKV_TRACE)
+    make -C mechta_b200/csrc measure                       # builds mechta_b200/libmechta_kv_measure.so (-DMKV_MEASURE)
     python -m mechta_b200.trace_timeline --context 65536   # timeline + microseconds per launch
     python -m mechta_b200.trace_timeline --context 262144 --no-trace   # stock library, per-launch time only
 
-The trace build makes every CTA of verify_f16_tc_kernel record %globaltimer at its start, after
+The measurement build makes every CTA of verify_f16_tc_kernel record %globaltimer at its start, after
 griddepcontrol.wait, at each batch of MMAs, when its piece is written, in the merge and at its exit. The loop is
 the benchmark's: per step one append of 4 rows to all layers, then one verify launch per layer, nothing between
 the launches. Times are medians over the CTAs of one launch, in microseconds from the launch's first CTA start.
@@ -36,9 +36,9 @@ def main() -> None:
     import torch
     from mechta_b200 import _lib
     if not args.no_trace:
-        so = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libmechta_kv_trace.so")
+        so = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libmechta_kv_measure.so")
         if not os.path.exists(so):
-            raise SystemExit("build the trace library first: make -C mechta_b200/csrc trace")
+            raise SystemExit("build the trace library first: make -C mechta_b200/csrc measure")
         _lib.SO_PATH = so
     from mechta_b200 import kv
 

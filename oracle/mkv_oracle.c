@@ -22,6 +22,16 @@ int mko_threads(void) {
 #endif
 }
 
+/* Threads of the parallel regions that follow, whatever OMP_NUM_THREADS said when the library was loaded (launchers such
+ * as torch.distributed.run export OMP_NUM_THREADS=1 to every rank). n < 1 leaves the setting alone. */
+void mko_set_threads(int n) {
+#ifdef _OPENMP
+    if (n >= 1) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 /* ---- M/engine.rs:108-114 ------------------------------------------------------------------------ */
 void mko_rope_table(int32_t pos, float out[64]) {
     const float scale = powf(1e7f, -2.0f / 64.0f);

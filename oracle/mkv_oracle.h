@@ -115,6 +115,7 @@ uint64_t mko_root_key(const uint32_t *tok, size_t n);
 
 /* number of OpenMP threads the attention routines use (1 if built without) */
 int mko_threads(void);
+void mko_set_threads(int n);
 
 #ifdef __cplusplus
 }

@@ -60,6 +60,7 @@ def lib() -> C.CDLL:
         L.mko_attn_gate.argtypes = [vp, vp, u32, vp]
         L.mko_attn_window_f64.argtypes = [i32, vp, vp, u32, u32, vp, u32, u32, vp, vp]
         L.mko_threads.restype = i32
+        L.mko_set_threads.argtypes = [i32]
         _lib = L
     return _lib
 
@@ -221,6 +222,14 @@ def root_key(tokens) -> int:
 
 def threads() -> int:
     return int(lib().mko_threads())
+
+
+def use_all_cores() -> int:
+    """Sets the OpenMP thread count to the cores this process may run on (a launcher may have exported
+    OMP_NUM_THREADS=1) and returns it."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().mko_set_threads(int(n))
+    return threads()
 
 
 def max_rel(a: np.ndarray, b: np.ndarray) -> float:

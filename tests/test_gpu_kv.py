@@ -62,6 +62,10 @@ def test_append_bit_exact(ctx, oracle, fmt, ntok):
     v = synth.normal(21, synth.S_VNEW, ntok, (ntok, 2, 256)) * 4.0
     k[0, 0, :6] = [70000.0, -70000.0, 1e-7, 6e-8, 2.0**-24, 65519.0]  # overflow, subnormals, ties
     tab = kv.rope_table(pos, ntok)
+    with pytest.raises(_lib.MkvError) as e:  # rows [0, pos) were never written: an append there would make them 'valid'
+        cache.append(1, pos, dev(k), dev(v), dev(tab))
+    assert e.value.status == _lib.ERR_STATE and len(cache) == 0
+    cache.set_len(pos)  # the host vouches for the (zero) rows below
     cache.append(1, pos, dev(k), dev(v), dev(tab))
     kc, vc = oracle.new_cache(int(fmt), 4096), oracle.new_cache(int(fmt), 4096)
     oracle.append(int(fmt), kc, vc, pos, k, v, tab)
@@ -80,6 +84,7 @@ def test_append_without_table_and_all_layers(ctx, oracle, fmt):
     k = synth.normal(22, synth.S_KNEW, 0, (n_layers, ntok, 2, 256))
     v = synth.normal(22, synth.S_VNEW, 0, (n_layers, ntok, 2, 256))
     tab = kv.rope_table(pos, ntok)
+    cache.set_len(pos)
     cache.append_layers(pos, dev(k), dev(v), dev(tab))
     for l in range(n_layers):
         kc, vc = oracle.new_cache(int(fmt), 4096), oracle.new_cache(int(fmt), 4096)
@@ -261,9 +266,11 @@ def test_steady_state_steps_with_random_accepts(ctx, oracle, fmt):
     cache.close()
 
 
-@pytest.mark.parametrize("fmt,ctx_len", [(kv.KvFormat.F16, 65536), (kv.KvFormat.F32, 32768), (kv.KvFormat.F32, 131072)])
+@pytest.mark.parametrize("fmt,ctx_len", [(kv.KvFormat.F16, 65536), (kv.KvFormat.F32, 32768), (kv.KvFormat.F32, 131072),
+                                         (kv.KvFormat.F32, 261120), (kv.KvFormat.F16, 261120)])
 def test_verify_full_size_against_oracle(ctx, oracle, fmt, ctx_len):
-    """One layer at the benchmark's context length against the oracle, plus linearity in V."""
+    """One layer at the benchmark's context lengths (65,536 tokens; the last rows of a 262,144-token context) against the
+    oracle, plus linearity in V."""
     cache = kv.KvCache(ctx, fmt, 1, ctx_len + 1024)
     pos = ctx_len
     kc, vc = fill_both(oracle, cache, 0, pos + 4, 61, chunk=4096)
@@ -303,8 +310,11 @@ def test_chained_launches_equal_synchronised_launches(ctx):
     vn = torch.randn(steps, n_layers, 4, 2, 256, device="cuda", generator=g)
     acc = synth.accept_counts(72, steps)
 
+    cache.set_len(n)
+    ctx.sync()
+
     def run(sync_each):
-        cache.set_len(n)
+        cache.truncate(n)
         pos, outs = n, torch.empty(steps, n_layers, 4, 16, 256, device="cuda")
         for s in range(steps):
             cache.append_layers(pos, kn[s], vn[s], dev(kv.rope_table(pos, 4)))
@@ -483,6 +493,45 @@ def test_ring_cache_limits(ctx):
     cache.close()
 
 
+@pytest.mark.parametrize("fmt", FMTS)
+def test_fused_step_on_a_ring_cache_that_has_wrapped(ctx, oracle, fmt):
+    """mkv_attn_step on a ring cache: once the positions have gone round the ring, a step whose keys no longer fit it is
+    refused (and leaves the length alone); one that fits gives the attention over the ring's rows."""
+    ring, eps = 1024, 1e-6
+    cache = kv.KvCache(ctx, fmt, 1, 8192, ring=ring)
+    kc, vc = oracle.new_cache(int(fmt), ring), oracle.new_cache(int(fmt), ring)
+    pos = 2500  # two and a half turns
+    for p in range(0, pos, 500):
+        k = synth.normal(171, synth.S_K, p, (500, 2, 256)); v = synth.normal(171, synth.S_V, p, (500, 2, 256))
+        tab = kv.rope_table(p, 500)
+        cache.append(0, p, dev(k), dev(v), dev(tab))
+        oracle.append_ring(int(fmt), kc, vc, ring, p, k, v, tab)
+    ntok = 4
+    qf, kb, vb, qw, kw, _ = synth.step_inputs(172, ntok)
+    tab = kv.rope_table(pos, ntok)
+    out = torch.full((ntok, 16, 256), 5.0, device="cuda")
+    with pytest.raises(_lib.MkvError) as e:  # first_pos 0: 2,504 keys do not fit 1,024 rows
+        cache.attn_step(0, 0, pos, dev(qf), dev(kb), dev(vb), dev(qw), dev(kw), dev(tab), out, None, eps)
+    assert e.value.status == _lib.ERR_CAPACITY and len(cache) == pos
+    first = pos + ntok - ring  # the oldest position the ring still holds once the step's rows are in
+    cache.attn_step(0, first, pos, dev(qf), dev(kb), dev(vb), dev(qw), dev(kw), dev(tab), out, None, eps)
+    ctx.sync()
+    assert len(cache) == pos + ntok
+    qn = oracle.rmsnorm(qf, 16 * ntok, 256, 512, qw, eps)
+    kn = oracle.rmsnorm(kb, 2 * ntok, 256, 256, kw, eps)
+    qr = oracle.rope2(qn, 16, tab).reshape(ntok, 16, 256)
+    oracle.append_ring(int(fmt), kc, vc, ring, pos, kn.reshape(ntok, 2, 256), vb.reshape(ntok, 2, 256), tab)
+    gk, gv = host_bits(cache, 0)
+    assert np.array_equal(gk, kc) and np.array_equal(gv, vc)
+    # token t sees keys first..pos + t: a window of pos + t - first + 1 positions that moves with the token, so compare
+    # token by token against the windowed f64 reference
+    got = out.cpu().numpy()
+    for t in range(ntok):
+        want = oracle.attn_window_f64(int(fmt), kc, vc, ring, pos + t - first + 1, None, pos + t, qr[t:t + 1])
+        assert oracle.max_rel(got[t:t + 1], oracle.attn_gate(want.astype(np.float32), qf[t:t + 1])) < TOL[fmt]
+    cache.close()
+
+
 # ---------------------------------------------------------------- shards and batches ----------------------------
 
 @pytest.mark.parametrize("fmt", FMTS)
@@ -561,7 +610,75 @@ def test_ragged_batch_of_sessions(ctx, oracle, fmt):
         c.close()
 
 
+def test_ragged_batch_at_full_lengths(ctx, oracle):
+    """Eight sessions with lengths up to 131,072 (the multi-session configuration's range) in one launch per layer, each
+    against the oracle."""
+    fmt = kv.KvFormat.F16
+    lens = [131072 - 8, 1024, 100000, 65536, 7777, 32768 + 5, 2048, 50001]
+    caches, ocs, qs, outs = [], [], [], []
+    for i, n in enumerate(lens):
+        c = kv.KvCache(ctx, fmt, 1, max(kv.CTX_MIN, min(kv.CTX_MAX, (n + 4 + 1023) // 1024 * 1024 + 1024)))
+        ocs.append(fill_both(oracle, c, 0, n + 4, 180 + i, chunk=8192))
+        caches.append(c)
+        qs.append(synth.normal(180 + i, synth.S_Q, 0, (4, 16, 256)))
+        outs.append(torch.full((4, 16, 256), float("nan"), device="cuda"))
+    dq = [dev(q) for q in qs]
+    ctx.attn_verify_batch([(caches[i], 0, 0, lens[i], dq[i], outs[i]) for i in range(len(lens))])
+    ctx.sync()
+    for i in range(len(lens)):
+        want = oracle.attn_ref_f32(int(fmt), ocs[i][0], ocs[i][1], 0, lens[i], qs[i])
+        err = oracle.max_rel(outs[i].cpu().numpy(), want)
+        assert err < TOL[fmt], (lens[i], err)
+    for c in caches:
+        c.close()
+
+
 # ---------------------------------------------------------------- prefill ------------------------------------
+
+def test_prefix_restore_prefill_snapshot_at_full_size(ctx, oracle):
+    """The prefix-cache configuration at its own size: a 32,768-row f16 snapshot is restored, a 2,048-token block is
+    appended and attends to the prefix and to itself (544 key tiles for the last tokens), and the 34,816 rows are
+    snapshotted back. Order of the reference: write_root (engine.rs:804-823), writers of the whole block, attention
+    (engine.rs:1213-1226), read_root (engine.rs:784-802). Attention against the oracle on tokens at the block's ends,
+    group borders and middle, with f32 and with f16 queries; the snapshot bytes against the oracle's."""
+    fmt = kv.KvFormat.F16
+    n_layers, prefix, block = 2, 32768, 2048
+    kcs = [oracle.new_cache(int(fmt), prefix + block) for _ in range(n_layers)]
+    vcs = [oracle.new_cache(int(fmt), prefix + block) for _ in range(n_layers)]
+    for l in range(n_layers):
+        for p in range(0, prefix, 8192):
+            oracle.append(int(fmt), kcs[l], vcs[l], p, synth.normal(190 + l, synth.S_K, p, (8192, 2, 256)),
+                          synth.normal(190 + l, synth.S_V, p, (8192, 2, 256)), kv.rope_table(p, 8192))
+    snap = oracle.snapshot(int(fmt), kcs, vcs, prefix)
+    cache = kv.KvCache(ctx, fmt, n_layers, prefix + block)
+    payload = torch.from_numpy(snap).pin_memory()
+    cache.write_root(kv.Root(prefix, fmt, n_layers, payload))
+    assert len(cache) == prefix
+    kn = synth.normal(192, synth.S_KNEW, 0, (n_layers, block, 2, 256))
+    vn = synth.normal(192, synth.S_VNEW, 0, (n_layers, block, 2, 256))
+    tab = kv.rope_table(prefix, block)
+    cache.append_layers(prefix, dev(kn), dev(vn), dev(tab))
+    for l in range(n_layers):
+        oracle.append(int(fmt), kcs[l], vcs[l], prefix, kn[l], vn[l], tab)
+    toks = [0, 1, 15, 16, 1023, 2046, 2047]
+    for l in range(n_layers):
+        q = synth.normal(193 + l, synth.S_Q, 0, (block, 16, 256))
+        out = torch.full((block, 16, 256), float("nan"), device="cuda")
+        cache.attn_prefill(l, 0, prefix, dev(q), out)
+        out16 = torch.full((block, 16, 256), float("nan"), device="cuda")
+        cache.attn_prefill(l, 0, prefix, dev(q).half(), out16)
+        ctx.sync()
+        got, got16 = out.cpu().numpy(), out16.cpu().numpy()
+        assert np.isfinite(got).all() and np.isfinite(got16).all()
+        want = oracle.attn_ref_f32_sel(int(fmt), kcs[l], vcs[l], 0, prefix, toks, q)
+        err = oracle.max_rel(got[toks], want)
+        assert err < TOL[fmt], err
+        # the kernel rounds f32 queries to f16 itself (the reference's q_f16 pass): the f16 input gives the same bits
+        assert np.array_equal(got, got16)
+    root = cache.read_root(prefix + block)
+    assert np.array_equal(root.payload.numpy(), oracle.snapshot(int(fmt), kcs, vcs, prefix + block))
+    cache.close()
+
 
 @pytest.mark.parametrize("fmt", FMTS)
 @pytest.mark.parametrize("prefix,ntok,first", [(0, 64, 0), (0, 17, 0), (100, 8, 0), (1000, 512, 0), (1000, 128, 300),
@@ -689,6 +806,69 @@ def test_dispatch_with_reference_uniforms(ctx, oracle):
     with pytest.raises(_lib.MkvError) as e:
         cache.dispatch(0, "delta_q", [0] * 8)
     assert e.value.status == _lib.ERR_UNSUPPORTED
+    cache.close()
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+def test_dispatch_of_the_prefill_list(ctx, oracle, fmt):
+    """The attention branch of block_n (engine.rs:1213-1241) with the uniforms of inputs_n (engine.rs:915-927): writers of
+    the whole block, q_f16 + attn_fa_mx (f16 cache) or attn_fa (f32 cache) per group of 64 tokens and split of chunks with
+    the attn_fd_combine after each group; then a block of 8 through attn_fd4."""
+    import struct
+    scale_bits = struct.unpack("<I", struct.pack("<f", 1.0 / 16.0))[0]
+    f16 = fmt == kv.KvFormat.F16
+    context, pos, nb = 4096, 1000, 128
+    cache = kv.KvCache(ctx, fmt, 1, context)
+    kc, vc = fill_both(oracle, cache, 0, pos, 160)
+    k = synth.normal(160, synth.S_KNEW, 0, (nb, 2, 256)); v = synth.normal(160, synth.S_VNEW, 0, (nb, 2, 256))
+    q = synth.normal(160, synth.S_Q, 0, (nb, 16, 256))
+    tab = kv.rope_table(pos, nb)
+    cache.dispatch(0, "kv_rope2" if f16 else "rope2", [256, 2 * nb, 0, 0, 256, 256, 2, pos * 512], dev(k), dev(tab))
+    assert len(cache) == pos  # the rows count once their V half is written
+    cache.dispatch(0, "kv_copy" if f16 else "copy", [nb * 512, 0, 0, 0, 0, 0, 0, pos * 512], dev(v))
+    assert len(cache) == pos + nb
+    oracle.append(int(fmt), kc, vc, pos, k, v, tab)
+    gk, gv = host_bits(cache, 0)
+    assert np.array_equal(gk, kc) and np.array_equal(gv, vc)
+    att = torch.full((nb, 16, 256), float("nan"), device="cuda")
+    qr = dev(q)
+    fa_ch, fa_split = 2048, 8
+    n_splits = -(-(context // fa_ch) // fa_split)
+    if f16:
+        qh = torch.empty(nb, 16, 256, device="cuda", dtype=torch.float16)
+        cache.dispatch(0, "q_f16", [nb * 2048, 0, 0, 0, 0, 0, 0, 0], qr, None, qh)
+        assert torch.equal(qh, qr.half())
+    for g in range(nb // 64):
+        u0 = None
+        for sp in range(n_splits):
+            u = [pos + 1, context // fa_ch, scale_bits, 0, g * 64, sp * fa_split, fa_ch, 0]
+            u0 = u0 or u
+            cache.dispatch(0, "attn_fa_mx" if f16 else "attn_fa", u, qh if f16 else qr, None, att)
+        cache.dispatch(0, "attn_fd_combine", u0, None, None, att)
+    ctx.sync()
+    got = att.cpu().numpy()
+    assert np.isfinite(got).all()
+    toks = [0, 1, 63, 64, 100, 127]
+    assert oracle.max_rel(got[toks], oracle.attn_ref_f32_sel(int(fmt), kc, vc, 0, pos, toks, q)) < TOL[fmt]
+    # a block of 8 tokens after it: attn_fd4, one dispatch per 8 tokens (engine.rs:1237-1241, uniform engine.rs:920-922)
+    pos2, nb2 = pos + nb, 8
+    k2 = synth.normal(161, synth.S_KNEW, 0, (nb2, 2, 256)); v2 = synth.normal(161, synth.S_VNEW, 0, (nb2, 2, 256))
+    q2 = synth.normal(161, synth.S_Q, 0, (nb2, 16, 256))
+    tab2 = kv.rope_table(pos2, nb2)
+    cache.dispatch(0, "kv_rope2" if f16 else "rope2", [256, 2 * nb2, 0, 0, 256, 256, 2, pos2 * 512], dev(k2), dev(tab2))
+    cache.dispatch(0, "kv_copy" if f16 else "copy", [nb2 * 512, 0, 0, 0, 0, 0, 0, pos2 * 512], dev(v2))
+    oracle.append(int(fmt), kc, vc, pos2, k2, v2, tab2)
+    att2 = torch.full((nb2, 16, 256), float("nan"), device="cuda")
+    u4 = [pos2 + 1, context // 64, scale_bits, 0, 0, 0, 64, 0]
+    cache.dispatch(0, "attn_fd4", u4, dev(q2), None, att2)
+    cache.dispatch(0, "attn_fd_combine", u4, None, None, att2)
+    ctx.sync()
+    want2 = oracle.attn_ref_f32_sel(int(fmt), kc, vc, 0, pos2, list(range(nb2)), q2)
+    assert oracle.max_rel(att2.cpu().numpy(), want2) < TOL[fmt]
+    # a writer whose rows would leave a gap is refused like mkv_append
+    with pytest.raises(_lib.MkvError) as e:
+        cache.dispatch(0, "kv_rope2" if f16 else "rope2", [256, 8, 0, 0, 256, 256, 2, (pos2 + 100) * 512], dev(k2), dev(tab2))
+    assert e.value.status == _lib.ERR_STATE
     cache.close()
 
 
