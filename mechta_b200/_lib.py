@@ -10,7 +10,8 @@ import os
 import subprocess
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-SO_PATH = os.path.join(_HERE, "libmechta_kv.so")
+# MKV_LIB_PATH names another build of the same library to load instead (e.g. the measurement build, `make measure`)
+SO_PATH = os.environ.get("MKV_LIB_PATH") or os.path.join(_HERE, "libmechta_kv.so")
 HEADER = os.path.join(os.path.dirname(_HERE), "include", "mechta_kv.h")
 
 OK, ERR_INVALID, ERR_CAPACITY, ERR_CUDA, ERR_NOMEM, ERR_UNSUPPORTED, ERR_STATE, ERR_FORMAT, ERR_IO = range(9)

@@ -86,18 +86,17 @@ static uint32_t measure_phase() {
 }
 
 void Cache::note_write(uint32_t pos) {
-    const uint64_t now = ctx->launches;
     size_t keep = 0;
     for (size_t i = 0; i < writes.size(); i++)
-        if (writes[i].first + WRITE_WINDOW > now && writes[i].first >= ctx->synced_launches) writes[keep++] = writes[i];
+        if (writes[i].launches + WRITE_WINDOW > ctx->launches && writes[i].syncs == ctx->syncs) writes[keep++] = writes[i];
     writes.resize(keep);
-    writes.push_back({now, pos});
+    writes.push_back({ctx->launches, ctx->syncs, pos});
 }
 
 uint32_t Cache::safe_below(uint32_t pos) const {
     uint32_t lo = pos;
     for (const auto &w : writes)
-        if (w.first + WRITE_WINDOW > ctx->launches && w.first >= ctx->synced_launches) lo = std::min(lo, w.second);
+        if (w.launches + WRITE_WINDOW > ctx->launches && w.syncs == ctx->syncs) lo = std::min(lo, w.pos);
     return lo;
 }
 
@@ -125,19 +124,14 @@ static mkv_status ensure_scratch(Cache *c, size_t pieces) {
     MKV_CUDA(cudaStreamSynchronize(ctx->stream));
     if (c->part_ml) cudaFree(c->part_ml);
     if (c->part_o) cudaFree(c->part_o);
-    if (c->part_flags) cudaFree(c->part_flags);
     c->part_ml = c->part_o = nullptr;
-    c->part_flags = nullptr;
     c->scratch_pieces = 0;
     if (cudaMalloc(&c->part_ml, pieces * 32 * 2 * sizeof(float)) != cudaSuccess ||
-        cudaMalloc(&c->part_o, pieces * 32 * 256 * sizeof(float)) != cudaSuccess ||
-        cudaMalloc(&c->part_flags, pieces * sizeof(uint32_t)) != cudaSuccess) {
+        cudaMalloc(&c->part_o, pieces * 32 * 256 * sizeof(float)) != cudaSuccess) {
         cudaGetLastError();
         set_error("out of device memory for %zu split-K pieces", pieces);
         return MKV_ERR_NOMEM;
     }
-    // a flag holds the number of the launch that wrote its piece; launch numbers start at 1
-    MKV_CUDA(cudaMemsetAsync(c->part_flags, 0, pieces * sizeof(uint32_t), ctx->stream));
     c->scratch_pieces = pieces;
     return MKV_OK;
 }
@@ -232,7 +226,6 @@ static mkv_status place_scratch(Cache *const *caches, VerifyItem *items, int n) 
         }
         items[i].part_ml = caches[i]->part_ml + before * 32 * 2;
         items[i].part_o = caches[i]->part_o + before * 32 * 256;
-        items[i].flags = caches[i]->part_flags + before;
     }
     return MKV_OK;
 }
@@ -383,7 +376,7 @@ mkv_status mkv_sync(mkv_ctx *h) {
     if (st != MKV_OK) return st;
     MKV_CUDA(cudaStreamSynchronize(ctx->stream));
     MKV_CUDA(cudaStreamSynchronize(ctx->copy_stream));
-    ctx->synced_launches = ctx->launches;
+    ctx->syncs++;
     return check_device_status(ctx);
 }
 
@@ -564,7 +557,6 @@ void mkv_cache_destroy(mkv_cache *h) {
     if (c->vptrs_dev) cudaFree(c->vptrs_dev);
     if (c->part_ml) cudaFree(c->part_ml);
     if (c->part_o) cudaFree(c->part_o);
-    if (c->part_flags) cudaFree(c->part_flags);
     if (c->qr) cudaFree(c->qr);
     if (c->ev_snapshot) cudaEventDestroy(c->ev_snapshot);
     Ctx *ctx = c->ctx;
@@ -771,7 +763,7 @@ mkv_status mkv_attn_step(mkv_cache *h, int layer, uint32_t first_pos, uint32_t p
         return MKV_ERR_STATE;
     }
     c->len = (uint32_t)end; // the rows this call writes count as valid for its own attention
-    c->note_write(pos);     // (a note that outlives a failed call only makes later launches more careful)
+    c->note_write(pos); // (a note that outlives a failed call only makes later launches more careful)
     // Everything that can refuse the call comes before the first launch; the length goes back on every failure.
     // fill_item wants an output pointer for its checks; the f16 one serves when there is no f32 output
     mkv_status st = fill_item(c, layer, first_pos, pos, ntok, c->qr, ag ? ag : static_cast<float *>(ag16), false, &it);

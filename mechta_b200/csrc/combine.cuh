@@ -3,19 +3,17 @@
 //
 // Arithmetic: attn_fd_combine of the reference (W/ops.wgsl:529-537) over this library's pieces:
 //   M = max_s m_s;  tot = sum_s e^(m_s - M) l_s;  acc[d] = sum_s e^(m_s - M) O_s[d];  out = acc / tot.
-// The sums run over the pieces in index order whatever the order of their arrival, so a result does not depend
-// on timing.
+// The sums run over the pieces in index order, so a result does not depend on timing.
 //
-// Scheduling. Every CTA writes its piece, publishes it (one flag word per piece, written with release semantics
-// and holding the launch's number) and takes a ticket from a counter in global memory. R = min(CTAs of the
-// item, 64) of them each merge a share of the item's 64 rows: the ones that arrive just BEFORE the last few. A
-// merging CTA gathers the pieces as their flags come up, so by the time the last piece is published everything
-// else is already in its registers and what is left after the last piece is one flag, one load and the sums.
-// (Letting the very last arrivals merge, as an arrival counter alone would suggest, puts the whole gather of
-// ~74 pieces per row behind the last piece.) A waiting CTA has finished its own tiles, there are at most 64 of
-// them and the grid is planned to fit the SMs in one wave, so the CTAs they wait for always run; every wait is
-// bounded all the same. Items whose pieces carry no flags (flags == null: the allocation-free entry point) use
-// the counter alone: the last R arrivals wait until it shows that all pieces are there.
+// Scheduling. Every CTA writes its piece and publishes it: the threads that wrote it meet at a barrier, one of
+// them issues a release fence and takes a ticket from a counter in global memory. The last R = min(CTAs of the
+// item, 64) arrivals wait (bounded) until the counter shows that all pieces are there, and each merges a share of
+// the item's 64 rows. Only CTAs that have finished their own work ever wait, and fewer of them than there are SMs,
+// so the others always make progress; the earlier arrivals leave at once, which lets the CTAs of the next launch
+// in the stream start on their SMs and load their first tiles.
+// (Measured against this: per-piece flags with merging CTAs that gather the pieces as they land, whole rows or
+// half rows per CTA. The CTAs that wait hold their SMs, the next launch's CTAs start later and find their first
+// tiles not yet loaded when they may begin: 3 to 4 % slower at 65,536 tokens.)
 //
 // Sequence shards on several GPUs (`push` set): the merged rows are this rank's record. The merging CTA stores
 // each row straight into every rank's mailbox (plain peer stores over NVLink, no multicast), raises that row's
@@ -40,7 +38,8 @@ __device__ __forceinline__ const VerifyItem &pick_item(const VerifyItem *items, 
 
 constexpr int FIN_MAX_THREADS = 512;
 constexpr long long FIN_WAIT_LIMIT = 4000000000ll; // about two seconds of SM clocks
-constexpr uint32_t FIN_LATE = 20;                  // the last arrivals that do not merge (when there are enough CTAs)
+constexpr uint32_t FIN_JOBS = 64;                  // one job per row (kvh * 32 + row) of the item
+constexpr uint32_t FIN_COLS = 64;                  // float4 columns of a row
 
 struct FinishSmem {
     float e_s[MAX_SPLITS];
@@ -48,20 +47,27 @@ struct FinishSmem {
     float tot, M;
     uint32_t ticket, ok;
 #ifdef MKV_TRACE
-    unsigned long long tr[3]; // ticket taken, all pieces seen, rows merged
-    unsigned long long tm[4]; // inside the merge of a row: loads issued, maximum known, pieces summed, row written
+    unsigned long long tr[3]; // ticket taken, all pieces published, rows merged
+    unsigned long long tm[4]; // inside the merge of a row: loads issued, maximum known, pieces summed
 #endif
-    float4 part[FIN_MAX_THREADS / 64][64];
+    float4 part[FIN_MAX_THREADS / FIN_COLS][FIN_COLS];
 };
 
+// Publishes the calling CTA's piece and returns its ticket (arrival number within the item). Called by ONE thread,
+// after a barrier that every thread which wrote part of the piece has passed.
+__device__ __forceinline__ uint32_t publish_piece(const VerifyItem &it) {
+    ptx::fence_acq_rel_gpu(); // the piece (all threads' stores, ordered before this by the barrier) precedes the ticket
+    return atomicAdd(it.counter, 1u) - it.ticket_base;
+}
+
 // Row rr (= tok * 16 + head) of this rank's record has just been stored into every rank's mailbox by the threads
-// of this CTA. Raises the row's flag everywhere, waits for the same row of every other rank and merges the
-// ranks' rows into out[rr][256]. All NT threads of the CTA call this. On a wait that runs out the status word
-// is set and the output is left alone.
+// of this CTA. Raises the row's flag everywhere, waits for the same row of every other rank and merges the ranks'
+// rows into out[rr][256]. All NT threads of the CTA call this. On a wait that runs out the status word is set and
+// the output is left alone.
 template <int NT>
 __device__ __forceinline__ bool exchange_row(const PushInfo &P, uint32_t epoch, uint32_t rr, float *out, uint32_t *status) {
     const uint32_t tid = threadIdx.x, par = epoch & 1u, world = P.world;
-    __syncthreads(); // the row's stores of all threads precede the releases below
+    __syncthreads(); // the stores of all threads precede the releases below
     if (tid < world && P.rowflag[par][tid]) ptx::st_release_sys(P.rowflag[par][tid] + rr, epoch);
     bool ok = true;
     if (tid < world) {
@@ -95,14 +101,13 @@ __device__ __forceinline__ bool exchange_row(const PushInfo &P, uint32_t epoch, 
     return true;
 }
 
-// One row (kvh * 32 + row) of one item, by all NT threads of the CTA.
-// GATHER: the pieces may still be arriving; a piece is read once its flag shows this launch's number.
-// Otherwise all pieces are known to be in global memory.
+// One row (kvh * 32 + row) of one item, by all NT threads of the CTA; all pieces are in global memory.
 // EXT = false compiles the sink handling out (the kernels of the plain path are instantiated without it).
-template <int NT, bool EXT, bool GATHER>
+template <int NT, bool EXT>
 __device__ __forceinline__ void merge_row(const VerifyItem &it, uint32_t r, FinishSmem &sm, uint32_t *status) {
-    constexpr int GROUPS = NT / 64;
+    constexpr int GROUPS = NT / FIN_COLS;
     constexpr int NW = NT / 32;
+    constexpr int RND = (MAX_SPLITS + GROUPS - 1) / GROUPS; // pieces a thread may own: all in flight at once, one trip to L2
     const uint32_t kvh = r >> 5, row = r & 31u, tok = row >> 3, head = 8u * kvh + (row & 7u);
     const uint32_t tid = threadIdx.x;
     if (tok >= it.ntok) {
@@ -112,66 +117,19 @@ __device__ __forceinline__ void merge_row(const VerifyItem &it, uint32_t r, Fini
     }
     const uint32_t ns = it.nsplit;
     const float2 *ml = reinterpret_cast<const float2 *>(it.part_ml) + (size_t)kvh * ns * 32u + row;
-    const uint32_t grp = tid >> 6, d4 = tid & 63u;
-    const float4 *po = reinterpret_cast<const float4 *>(it.part_o + ((size_t)kvh * ns * 32u + row) * 256u) + d4;
-    // A round is RND loads per thread, all in flight at once: with one CTA per SM on 148 SMs an item has 74
-    // pieces per KV head, which is one round; a second trip to L2 would cost as much as the whole merge.
-    constexpr int RND = 20;
+    const uint32_t grp = tid / FIN_COLS, c4 = tid % FIN_COLS;
+    const float4 *po = reinterpret_cast<const float4 *>(it.part_o + ((size_t)kvh * ns * 32u + row) * 256u) + c4;
     float4 x[RND];
     float m = NEG_BIG, l = 0.0f;
-    if (GATHER) {
-        // thread (grp, d4) owns pieces grp, grp + GROUPS, ...; thread tid < ns also owns (m, l) of piece tid
-        const uint32_t *fl = it.flags + (size_t)kvh * ns;
-        const uint32_t ep = it.epoch;
-        uint32_t pend = 0;
+    if (tid < ns) { // (m, l) first: the maximum is needed before anything can be summed
+        const float2 y = __ldcg(ml + (size_t)tid * 32u);
+        m = y.x;
+        l = y.y;
+    }
 #pragma unroll
-        for (int i = 0; i < RND; i++) {
-            x[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (grp + GROUPS * (uint32_t)i < ns) pend |= 1u << i;
-        }
-        bool mlpend = tid < ns;
-        const long long t0 = clock64();
-        for (;;) {
-            uint32_t got = 0, f[RND];
-#pragma unroll
-            for (int i = 0; i < RND; i++) // the flag loads of a round are all in flight together
-                f[i] = ((pend >> i) & 1u) ? ptx::ld_relaxed_gpu(fl + grp + GROUPS * i) : ~ep;
-            const uint32_t fm = mlpend ? ptx::ld_relaxed_gpu(fl + tid) : ~ep;
-#pragma unroll
-            for (int i = 0; i < RND; i++)
-                if (f[i] == ep) got |= 1u << i;
-            const bool gm = fm == ep;
-            if (got != 0u || gm) {
-                __threadfence(); // with the relaxed flag loads above: acquire
-#pragma unroll
-                for (int i = 0; i < RND; i++)
-                    if ((got >> i) & 1u) x[i] = __ldcg(po + (size_t)(grp + GROUPS * i) * 2048u);
-                if (gm) {
-                    const float2 y = __ldcg(ml + (size_t)tid * 32u);
-                    m = y.x;
-                    l = y.y;
-                    mlpend = false;
-                }
-                pend &= ~got;
-            }
-            if (tid == 0 && clock64() - t0 > FIN_WAIT_LIMIT) sm.ok = 0u; // a piece never came
-            if (__syncthreads_and(pend == 0u && !mlpend)) break;
-            if (!sm.ok) {
-                if (tid == 0) atomicOr(status, DEV_ERR_WAIT_TIMEOUT);
-                return;
-            }
-        }
-    } else {
-        if (tid < ns) { // (m, l) first: the maximum is needed before anything can be summed
-            const float2 y = __ldcg(ml + (size_t)tid * 32u);
-            m = y.x;
-            l = y.y;
-        }
-#pragma unroll
-        for (int i = 0; i < RND; i++) {
-            const uint32_t s = grp + GROUPS * i;
-            x[i] = s < ns ? __ldcg(po + (size_t)s * 2048u) : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
+    for (int i = 0; i < RND; i++) { // thread (grp, c4) owns pieces grp, grp + GROUPS, ...
+        const uint32_t s = grp + GROUPS * i;
+        x[i] = s < ns ? __ldcg(po + (size_t)s * 2048u) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
 #ifdef MKV_TRACE
     if (tid == 0) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(sm.tm[0]));
@@ -209,33 +167,24 @@ __device__ __forceinline__ void merge_row(const VerifyItem &it, uint32_t r, Fini
         if (tid == 0) sm.tot = (EXT && it.sinks && !it.partial) ? y + expf(it.sinks[head] - sm.M) : y;
     }
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (uint32_t s0 = grp; s0 < ns; s0 += GROUPS * (uint32_t)RND) {
-        if (s0 != grp) { // later rounds (more pieces than one round holds; never with GATHER)
 #pragma unroll
-            for (int i = 0; i < RND; i++) {
-                const uint32_t s = s0 + GROUPS * i;
-                x[i] = s < ns ? __ldcg(po + (size_t)s * 2048u) : make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-        }
-#pragma unroll
-        for (int i = 0; i < RND; i++) {
-            const uint32_t s = s0 + GROUPS * i;
-            const float w = s < ns ? sm.e_s[s] : 0.0f;
-            acc.x += w * x[i].x;
-            acc.y += w * x[i].y;
-            acc.z += w * x[i].z;
-            acc.w += w * x[i].w;
-        }
+    for (int i = 0; i < RND; i++) {
+        const uint32_t s = grp + GROUPS * i;
+        const float w = s < ns ? sm.e_s[s] : 0.0f;
+        acc.x += w * x[i].x;
+        acc.y += w * x[i].y;
+        acc.z += w * x[i].z;
+        acc.w += w * x[i].w;
     }
-    sm.part[grp][d4] = acc;
+    sm.part[grp][c4] = acc;
     __syncthreads();
 #ifdef MKV_TRACE
     if (tid == 0) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(sm.tm[2]));
 #endif
-    if (tid < 64) {
+    if (tid < FIN_COLS) {
         float4 a = sm.part[0][tid];
 #pragma unroll
-        for (int g = 1; g < GROUPS; g++) {
+        for (int g = 1; g < GROUPS; g++) { // in group order: pieces g, g + GROUPS, ... were summed in index order above
             const float4 b = sm.part[g][tid];
             a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
         }
@@ -275,69 +224,56 @@ __device__ __forceinline__ void merge_row(const VerifyItem &it, uint32_t r, Fini
     }
 }
 
-// Called by every thread of every CTA of an item after the CTA's piece has been written to global memory.
-// `sm` must not alias anything still in use. Returns after this CTA's share of the merge (possibly none).
+// The CTA's share of the merge, given its ticket (publish_piece). Called by every thread of every CTA of an item;
+// `sm` must not alias anything still in use and nobody may have touched it since a barrier. Returns after this
+// CTA's rows (possibly none).
 template <int NT, bool EXT = true>
-__device__ __forceinline__ void finish_item(const VerifyItem &it, FinishSmem &sm, uint32_t *status) {
+__device__ __forceinline__ void finish_item(const VerifyItem &it, FinishSmem &sm, uint32_t *status, uint32_t ticket) {
     const uint32_t total = 2u * it.nsplit;
-    // A round of gathered loads holds 20 pieces per group of 64 threads; items with more pieces per KV head (never
-    // planned on a B200) and items without flags announce their pieces by the counter alone.
-    const bool gather = it.flags != nullptr && it.nsplit <= (uint32_t)(NT / 64) * 20u;
-    __syncthreads(); // every thread's part of the piece precedes thread 0's release below
+    const uint32_t R = total < FIN_JOBS ? total : FIN_JOBS;
+    if (ticket < total - R) return; // not among the last R: nothing to merge
     if (threadIdx.x == 0) {
-        if (gather) {
-            const uint32_t local = blockIdx.x - it.cta_begin; // piece (kvh, split) = (local & 1, local >> 1)
-            ptx::st_release_gpu(it.flags + (size_t)(local & 1u) * it.nsplit + (local >> 1), it.epoch);
-            sm.ticket = atomicAdd(it.counter, 1u) - it.ticket_base;
-        } else {
-            sm.ticket = ptx::atom_add_release_gpu(it.counter, 1u) - it.ticket_base;
-        }
-        sm.ok = 1u;
 #ifdef MKV_TRACE
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(sm.tr[0]));
         sm.tr[1] = sm.tr[2] = 0;
 #endif
-    }
-    __syncthreads();
-    const uint32_t ticket = sm.ticket;
-    const uint32_t R = total < 64u ? total : 64u;
-    const uint32_t late = gather ? (total - R < FIN_LATE ? total - R : FIN_LATE) : 0u;
-    const uint32_t first = total - R - late; // tickets [first, first + R) merge
-    if (ticket < first || ticket >= first + R) return;
-    if (!gather) {
-        if (threadIdx.x == 0) {
-            // wait until every CTA of the item has published; bounded, in case a CTA never arrives
-            const long long t0 = clock64();
-            bool ok = true;
-            while (ptx::ld_acquire_gpu(it.counter) - it.ticket_base < total) {
-                __nanosleep(32);
-                if (clock64() - t0 > FIN_WAIT_LIMIT) {
-                    ok = false;
-                    break;
-                }
+        // wait until every CTA of the item has published; bounded, in case a CTA never arrives
+        const long long t0 = clock64();
+        bool ok = true;
+        while (ptx::ld_acquire_gpu(it.counter) - it.ticket_base < total) {
+            __nanosleep(32);
+            if (clock64() - t0 > FIN_WAIT_LIMIT) {
+                ok = false;
+                break;
             }
-            if (!ok) atomicOr(status, DEV_ERR_WAIT_TIMEOUT);
-            sm.ok = ok ? 1u : 0u;
+        }
+        if (!ok) atomicOr(status, DEV_ERR_WAIT_TIMEOUT);
+        sm.ok = ok ? 1u : 0u;
 #ifdef MKV_TRACE
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(sm.tr[1]));
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(sm.tr[1]));
 #endif
-        }
-        __syncthreads();
+    }
+    __syncthreads(); // thread 0's acquire, passed on by the barrier, orders the piece loads (which bypass L1) behind the publications
+    if (!sm.ok) return;
+    for (uint32_t r = ticket - (total - R); r < FIN_JOBS; r += R) {
+        merge_row<NT, EXT>(it, r, sm, status);
         if (!sm.ok) return;
-        for (uint32_t r = ticket - first; r < 64u; r += R) {
-            merge_row<NT, EXT, false>(it, r, sm, status);
-            if (!sm.ok) return;
-        }
-    } else {
-        for (uint32_t r = ticket - first; r < 64u; r += R) {
-            merge_row<NT, EXT, true>(it, r, sm, status);
-            if (!sm.ok) return;
-        }
     }
 #ifdef MKV_TRACE
     __syncthreads();
     if (threadIdx.x == 0) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(sm.tr[2]));
 #endif
+}
+
+// The same for kernels that publish here: every thread's part of the piece is written, then thread 0 publishes.
+template <int NT, bool EXT = true>
+__device__ __forceinline__ void finish_item(const VerifyItem &it, FinishSmem &sm, uint32_t *status) {
+    __syncthreads(); // every thread's part of the piece precedes thread 0's fence
+    if (threadIdx.x == 0) sm.ticket = publish_piece(it);
+    __syncthreads();
+    const uint32_t ticket = sm.ticket;
+    __syncthreads(); // (sm.ok is written next)
+    finish_item<NT, EXT>(it, sm, status, ticket);
 }
 
 } // namespace mkv

@@ -19,7 +19,7 @@ constexpr int TILE32 = 32;          // keys per tile, f32 cache
 constexpr float NEG_BIG = -3.0e38f; // mask value of the reference (W/ops.wgsl:339)
 constexpr float NEG_TEST = -1.0e38f;
 constexpr float SCALE = 1.0f / 16.0f; // M/quad.rs:286 bits(1/16)
-constexpr int MAX_SPLITS = 160;     // upper bound of split-K pieces per KV head of one item
+constexpr int MAX_SPLITS = 80;      // upper bound of split-K pieces per KV head of one item (what a merging CTA holds in registers)
 
 // status word written by kernels instead of trapping (bit set = what went wrong)
 enum : uint32_t { DEV_ERR_WAIT_TIMEOUT = 1u };
@@ -38,13 +38,13 @@ void set_error(const char *fmt, ...);
 // Peer exchange of shard records without a collective library: where a rank's merged record goes.
 constexpr int MAX_PEERS = 8;
 constexpr size_t SLOT_FLOATS = 64 * 258; // one record [64 rows][258]
-constexpr size_t FLAG_WORDS = 64;        // one flag per record row
+constexpr size_t FLAG_WORDS = 64;        // one flag per row of a record
 struct PushInfo {
     float *slot[2][MAX_PEERS];       // [epoch parity][destination rank]: this rank's record [64][258] in that rank's mailbox
-    uint32_t *rowflag[2][MAX_PEERS]; // [epoch parity][destination rank]: this rank's 64 row flags there (a flag holds the epoch
-                                     // once the row of the record is complete)
+    uint32_t *rowflag[2][MAX_PEERS]; // [epoch parity][destination rank]: this rank's FLAG_WORDS flags there (a flag holds the
+                                     // epoch once that row of the record is complete)
     const float *inbox[2];           // this rank's own mailbox: [epoch parity] -> records [world][64][258]
-    const uint32_t *inflag[2];       // and their row flags [world][64]
+    const uint32_t *inflag[2];       // and their flags [world][FLAG_WORDS]
     uint32_t world;
 };
 
@@ -68,9 +68,6 @@ struct VerifyItem {
     uint32_t partial;   // 1: write the un-normalised record instead of the final output
     uint32_t *counter;  // arrival counter of this item's CTAs (global memory), never reset
     uint32_t ticket_base; // value of the counter before this launch
-    uint32_t *flags;    // [2][nsplit] one word per piece: holds `epoch` once the piece of this launch is in global memory;
-                        // null = the pieces are announced by the counter alone (the allocation-free entry point)
-    uint32_t epoch;     // this launch's number on its context (never 0)
     const PushInfo *push; // partial mode only: the record's rows go to every rank's mailbox, the rows of all ranks are
                           // merged here and `out` gets the final output
     uint32_t push_world;  // number of ranks (host copy of push->world)
@@ -122,8 +119,7 @@ struct Ctx {
     cudaEvent_t ev_copy = nullptr;    // copy -> compute ordering
     uint32_t *dev_status = nullptr;   // device status word
     uint64_t launches = 0;
-    uint32_t verify_epoch = 0;        // number of the last verify launch (VerifyItem::epoch)
-    uint64_t synced_launches = 0;     // value of `launches` at the last mkv_sync: everything launched before it has finished
+    uint64_t syncs = 0;               // mkv_sync calls so far: what was enqueued before the last of them has finished
     bool pdl = true; // programmatic dependent launch of the attention kernels (MKV_PDL=0 switches it off)
     // profiling of the attention core kernels
     bool prof = false;
@@ -154,14 +150,18 @@ struct Cache {
     uint32_t shard_first = 0;
     bool whole = true;     // holds the whole context (not a sequence shard)
     uint32_t len = 0; // global position after the last valid row
-    // Lowest position the recent writers (append, restore, scrub, the host) touched, each with the number of the
-    // context's launch it came before. An attention kernel may load tiles below all of them before the kernels
+    // Lowest position the recent writers (append, restore, scrub, the host) touched, each with the number of launches
+    // the context had made by then and the number of mkv_sync calls it had seen. An attention kernel may load tiles below all of them before the kernels
     // in front of it have finished: with programmatic dependent launch a whole chain of small launches can be
     // resident at once, so the writer just in front is not the only one that may still be running. Each
     // attention CTA fills an SM's shared memory, so at most one per SM can be resident and the chain is shorter
-    // than WRITE_WINDOW launches. Writers launched before the context's last mkv_sync have finished and are dropped.
+    // than WRITE_WINDOW launches. Writers noted before the context's last mkv_sync have finished and are dropped.
     static constexpr uint64_t WRITE_WINDOW = 160;
-    std::vector<std::pair<uint64_t, uint32_t>> writes;
+    struct Write {
+        uint64_t launches, syncs;
+        uint32_t pos;
+    };
+    std::vector<Write> writes;
     void note_write(uint32_t pos);
     uint32_t safe_below(uint32_t pos) const;
     size_t elem = 2;
@@ -174,7 +174,6 @@ struct Cache {
     float *qr = nullptr;             // [4][16][256] normalised and rotated queries of mkv_attn_step (stream-ordered)
     float *part_ml = nullptr;        // split-K scratch, shared by the layers (stream-ordered), grow-only
     float *part_o = nullptr;
-    uint32_t *part_flags = nullptr;  // one word per piece, zeroed when allocated (see VerifyItem::flags)
     size_t scratch_pieces = 0;       // pieces (KV head x split) the scratch holds
     cudaEvent_t ev_snapshot = nullptr;
     bool snapshot_pending = false;

@@ -432,16 +432,17 @@ exchange_empty_kernel(const PushInfo *__restrict__ push, uint32_t epoch, float *
     pdl_wait(); // the mailbox parity is free only once the launch before last has finished
     const PushInfo &P = *push;
     for (uint32_t dd = 0; dd < P.world; dd++) {
-        float *base = P.slot[epoch & 1u][dd];
-        if (!base) continue; // a rank that never joined the exchange
-        for (uint32_t i = tid; i < (uint32_t)REC; i += 256u) base[(size_t)rr * REC + i] = i == 0 ? NEG_BIG : 0.0f;
+        float *rec = P.slot[epoch & 1u][dd];
+        if (!rec) continue; // a rank that never joined the exchange
+        rec += (size_t)rr * REC;
+        for (uint32_t i = tid; i < (uint32_t)REC; i += 256u) rec[i] = i == 0 ? NEG_BIG : 0.0f;
     }
     exchange_row<256>(P, epoch, rr, out, status);
 }
 
 mkv_status launch_exchange_empty(Ctx *ctx, const PushInfo *push, uint32_t epoch, uint32_t ntok, float *out) {
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(16u * ntok);
+    cfg.gridDim = dim3(16u * ntok); // one CTA per row of the record
     cfg.blockDim = dim3(256);
     cfg.stream = ctx->stream;
     cudaLaunchAttribute at[1];
@@ -509,9 +510,7 @@ mkv_status launch_verify(Ctx *ctx, mkv_fmt fmt, VerifyItem *items_host, int n, b
     }
     uint32_t total = 0;
     bool any_empty = false, ext = false; // ext: some item uses ring rows, a window or sinks
-    if (++ctx->verify_epoch == 0u) ctx->verify_epoch = 1u; // piece flags hold the launch's number; 0 = never written
     for (int i = 0; i < n; i++) {
-        items_host[i].epoch = ctx->verify_epoch;
         ext |= items_host[i].ring != 0 || items_host[i].win != 0 || items_host[i].sinks != nullptr;
         total += 2u * items_host[i].nsplit;
         any_empty |= items_host[i].nsplit == 0;

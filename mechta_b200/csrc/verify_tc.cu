@@ -80,6 +80,7 @@ __device__ __forceinline__ unsigned long long vt_now() {
 struct VtShared {
     uint32_t tmem_base;
     volatile uint32_t abort;
+    uint32_t ticket; // this CTA's arrival number within its item (publish_piece)
 #ifdef MKV_TRACE
     VtTrace trace;
 #endif
@@ -532,6 +533,11 @@ verify_f16_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
                 for (int r = 0; r < 32; r++) po[(size_t)r * 256u + 128u * mh + klane] = __uint_as_float(oc[r]);
             }
         }
+        // The piece is published by the threads that wrote it, before the CTA's teardown: what follows the last piece
+        // of a launch is the critical path of the next one. (After a wait that ran out the piece is not valid; it is
+        // published all the same so that nobody waits for it, and the status word says what happened.)
+        vt_bar_sync();
+        if (tid == 128u) sh->ticket = publish_piece(it);
     }
 
     // ---------------- teardown: nothing of this CTA may still be in flight, then free the tensor memory ----------------
@@ -555,8 +561,8 @@ verify_f16_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
     }
     __syncthreads();
 #endif
-    // the CTAs that finish last merge the pieces (scratch in the ring, which is drained by now)
-    finish_item<256, EXT>(it, *reinterpret_cast<FinishSmem *>(smem), status);
+    // this CTA's share of the merge, if its ticket gives it one (scratch in the ring, which is drained by now)
+    finish_item<256, EXT>(it, *reinterpret_cast<FinishSmem *>(smem), status, sh->ticket);
 #ifdef MKV_TRACE
     if (tid == 0) {
         const unsigned int n = atomicAdd(&g_vt_trace_n, 1u);
@@ -564,7 +570,7 @@ verify_f16_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
             const FinishSmem &fs = *reinterpret_cast<const FinishSmem *>(smem);
             unsigned int smid;
             asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-            rec.launch = it.ticket_base; rec.cta = blockIdx.x; rec.sm = smid; rec.nt = nt; rec.ticket = fs.ticket;
+            rec.launch = it.ticket_base; rec.cta = blockIdx.x; rec.sm = smid; rec.nt = nt; rec.ticket = sh->ticket;
             rec.fin_ticket = fs.tr[0]; rec.fin_seen = fs.tr[1]; rec.fin_merged = fs.tr[2];
             rec.fin_loads = fs.tm[0]; rec.fin_max = fs.tm[1]; rec.fin_summed = fs.tm[2];
             rec.exit_ = vt_now();

@@ -54,6 +54,7 @@ def main() -> None:
             k, v = cache.buffer_tensors(l)
             k.normal_(); v.normal_()
         cache.set_len(n)
+        ctx.sync()  # the rows are in place: later launches may load them early
         q = torch.randn(nl, 4, 16, 256, device="cuda")
         out = torch.empty_like(q)
         kn = torch.randn(nl, 4, 2, 256, device="cuda")
@@ -103,10 +104,11 @@ def main() -> None:
                   f"Q ready med {med('q_ready'):.2f} | first S^T med {med('st_issued0', full):.2f} | "
                   f"last O^T med {med(last, full):.2f} max {us(last, full).max():.2f} | last piece {us('piece').max():.2f} | "
                   f"exit med {med('exit'):.2f} max {us('exit').max():.2f}")
-            m = x[x[:, COL["fin_seen"]] > 0]
+            m = x[x[:, COL["ticket"]] >= len(x) - min(len(x), 64)]  # the last arrivals merge
             if len(m):
-                print(f"  {len(m)} merging CTAs: ticket med {med('fin_ticket', m):.2f} | all pieces seen med {med('fin_seen', m):.2f} | "
-                      f"loads issued med {med('fin_loads', m):.2f} | maximum known med {med('fin_max', m):.2f} | "
+                print(f"  {len(m)} merging CTAs: ticket med {med('fin_ticket', m):.2f} max {us('fin_ticket', m).max():.2f} | "
+                      f"all pieces published med {med('fin_seen', m):.2f} max {us('fin_seen', m).max():.2f} | "
+                      f"loads issued med {med('fin_loads', m):.2f} max {us('fin_loads', m).max():.2f} | maximum known med {med('fin_max', m):.2f} | "
                       f"pieces summed med {med('fin_summed', m):.2f} | merged med {med('fin_merged', m):.2f} max {us('fin_merged', m).max():.2f}")
             print("  first tile: scores seen %.2f | read and scaled %.2f | votes %.2f | maxima reduced %.2f | references moved %.2f | "
                   "weights start %.2f" % tuple(med(n, full) for n in ("t0_scores", "t0_scaled", "t0_votes", "t0_reduced", "t0_moved", "t0_weights")))

@@ -29,6 +29,48 @@ def test_library_exports_every_declared_symbol():
     assert b"sm_100a" in L.mkv_version()
 
 
+def _c_prototypes():
+    """name -> number of parameters, from the header."""
+    text = re.sub(r"/\*.*?\*/", "", open(_lib.HEADER).read(), flags=re.S)
+    out = {}
+    for m in re.finditer(r"\b(mkv_[a-z0-9_]+)\s*\(([^;{}]*?)\)\s*;", text):
+        args = " ".join(m.group(2).split())
+        out[m.group(1)] = 0 if args in ("", "void") else len(args.split(","))
+    return out
+
+
+def test_rust_sys_crate_declares_the_whole_abi():
+    """rust/mechta-kv-sys/src/lib.rs (the `-sys` crate a Rust host links; it could not be compiled where it was written)
+    against include/mechta_kv.h: the same entry points with the same number of arguments, the structs with the same
+    fields, and the file is what its generator writes from the header today."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    rs = open(os.path.join(root, "rust", "mechta-kv-sys", "src", "lib.rs")).read()
+    rust = {}
+    for m in re.finditer(r"pub fn (mkv_[a-z0-9_]+)\(([^)]*)\)", rs):
+        args = m.group(2).strip()
+        rust[m.group(1)] = 0 if not args else len(args.split(","))
+    c = _c_prototypes()
+    assert len(c) >= 45
+    assert set(rust) == set(c), f"missing in Rust: {sorted(set(c) - set(rust))}; unknown in Rust: {sorted(set(rust) - set(c))}"
+    for name, n in c.items():
+        assert rust[name] == n, f"{name}: {n} parameters in the header, {rust[name]} in the Rust declaration"
+    for sname, fields in (("mkv_verify_item", ["cache", "layer", "first_pos", "pos", "ntok", "q_dev", "out_dev"]),
+                          ("mkv_step_in", ["qf_dev", "kb_dev", "vb_dev", "q_norm_dev", "k_norm_dev", "rope_tab_dev", "eps"])):
+        body = re.search(r"#\[repr\(C\)\]\s*#\[derive\(Clone, Copy\)\]\s*pub struct %s \{(.*?)\}" % sname, rs, flags=re.S).group(1)
+        assert re.findall(r"pub (\w+):", body) == fields
+    # the ctypes table agrees on the parameter counts as well
+    for name, (_, argtypes) in _lib._SIGS.items():
+        assert len(argtypes) == c[name], name
+    gen = os.path.join(root, "rust", "mechta-kv-sys", "gen_bindings.py")
+    assert subprocess.run([sys.executable, gen, "--check"]).returncode == 0
+    # the safe wrapper only calls what the -sys crate declares
+    wrapper = open(os.path.join(root, "rust", "mechta-kv", "src", "lib.rs")).read()
+    used = set(re.findall(r"sys::(mkv_[a-z0-9_]+)\(", wrapper))
+    assert used and used <= set(rust)
+
+
 @pytest.mark.skipif(not NO_GPU, reason="checks the behaviour without a device")
 def test_no_device_is_an_error_not_a_fallback():
     h = C.c_void_p()
