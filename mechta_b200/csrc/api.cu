@@ -350,6 +350,8 @@ static void ctx_free(Ctx *ctx) {
     if (ctx->counters_dev) cudaFree(ctx->counters_dev);
     if (ctx->items_host) cudaFreeHost(ctx->items_host);
     if (ctx->dev_status) cudaFree(ctx->dev_status);
+    if (ctx->pf_scratch) cudaFree(ctx->pf_scratch);
+    if (ctx->pf_counters) cudaFree(ctx->pf_counters);
     if (ctx->ev_compute) cudaEventDestroy(ctx->ev_compute);
     if (ctx->ev_copy) cudaEventDestroy(ctx->ev_copy);
     if (ctx->copy_stream) cudaStreamDestroy(ctx->copy_stream);

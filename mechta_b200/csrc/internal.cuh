@@ -118,6 +118,8 @@ struct Ctx {
     cudaEvent_t ev_compute = nullptr; // compute -> copy ordering
     cudaEvent_t ev_copy = nullptr;    // copy -> compute ordering
     uint32_t *dev_status = nullptr;   // device status word
+    float *pf_scratch = nullptr;      // prefill: partials of items split over two CTAs (prefill_tc.cu), allocated on first use
+    uint32_t *pf_counters = nullptr;  // prefill: arrival counter per work item, zero between launches
     uint64_t launches = 0;
     uint64_t syncs = 0;               // mkv_sync calls so far: what was enqueued before the last of them has finished
     bool pdl = true; // programmatic dependent launch of the attention kernels (MKV_PDL=0 switches it off)

@@ -682,10 +682,13 @@ def test_prefix_restore_prefill_snapshot_at_full_size(ctx, oracle):
 
 @pytest.mark.parametrize("fmt", FMTS)
 @pytest.mark.parametrize("prefix,ntok,first", [(0, 64, 0), (0, 17, 0), (100, 8, 0), (1000, 512, 0), (1000, 128, 300),
-                                                (2048, 2048, 0)])
+                                                (2048, 2048, 0), (0, 4096, 0), (700, 3001, 130), (3000, 2400, 2999),
+                                                (3000, 512, 0), (7000, 128, 100), (5000, 700, 4990)])
 def test_prefill_over_cache(ctx, oracle, fmt, prefix, ntok, first):
-    """Token T of the block sees [first, prefix + T]; rows are appended first, as the reference does."""
-    cache = kv.KvCache(ctx, fmt, 1, 4096)
+    """Token T of the block sees [first, prefix + T]; rows are appended first, as the reference does. Blocks of up to about
+    880 tokens over a long enough prefix are the ones the f16 kernel cuts into equal tile ranges over all SMs (items split
+    over CTAs and merged); the largest have more work items than the GPU has SMs."""
+    cache = kv.KvCache(ctx, fmt, 1, 4096 if prefix + ntok <= 4096 else 8192)
     kc, vc = fill_both(oracle, cache, 0, prefix + ntok, 90 + ntok)
     q = synth.normal(90, synth.S_Q, ntok, (ntok, 16, 256))
     out = torch.full((ntok, 16, 256), float("nan"), device="cuda")
@@ -693,7 +696,8 @@ def test_prefill_over_cache(ctx, oracle, fmt, prefix, ntok, first):
     ctx.sync()
     got = out.cpu().numpy()
     assert np.isfinite(got).all()
-    toks = sorted(set([0, 1, ntok // 2, ntok - 2, ntok - 1]) & set(range(ntok))) if ntok > 64 else list(range(ntok))
+    toks = (sorted(set([0, 1, 15, 16, 17, ntok // 3, ntok // 2, ntok // 2 + 1, (2 * ntok) // 3, ntok - 17, ntok - 2, ntok - 1])
+                   & set(range(ntok))) if ntok > 64 else list(range(ntok)))
     want = oracle.attn_ref_f32_sel(int(fmt), kc, vc, first, prefix, toks, q)
     err = oracle.max_rel(got[toks], want)
     assert err < TOL[fmt], err
