@@ -38,8 +38,8 @@ N_LAYERS = 10
 KV_BYTES_F16, KV_BYTES_F32 = 2048, 4096  # K + V bytes per position per layer
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of verify_f16_tc_kernel at the decode65k shape, from an ncu
-# capture of that kernel (134.6 MB read + 4.7 MB written: split-K pieces and the output)
-NCU_TRAFFIC_BYTES_DECODE65K = 139_300_000
+# capture of that kernel (134.6 MB read + 4.2 MB written: split-K pieces and the output)
+NCU_TRAFFIC_BYTES_DECODE65K = 138_800_000
 REGIONS = 5
 
 
@@ -502,7 +502,7 @@ def run_other(args, workload):
             r = bw.measure_verify262k(ctx, stream, kv.KvFormat.F32 if args.f32 else kv.KvFormat.F16, steps=min(args.steps, 50))
             metric, dtype, scaling = "kv_read_gbps", "f32" if args.f32 else "f16", "weak"
         else:
-            r = bw.measure_prefill(ctx, stream, min(args.steps, 20), min(args.warmup, 3))
+            r = bw.measure_prefill(ctx, stream, min(args.steps, 20), min(args.warmup, 3), args.block)
             metric, dtype, scaling = "prefill_attn_tflops", "f16", "weak"
         if rank == 0:
             frac = r.get("frac", r.get("frac_per_gpu"))
@@ -550,6 +550,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-other", action="store_true", help="skip the short runs of the other configurations")
     ap.add_argument("--f32", action="store_true", help="verify262k only: the f32 cache")
+    ap.add_argument("--block", type=int, default=2048, help="prefill only: tokens of the prefill block (default 2048)")
     ap.add_argument("--context", type=int, default=0, help="longctx only: context tokens (default 262144); smaller for profiling")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"], help="how shard records travel between ranks")
     args = ap.parse_args()

@@ -170,11 +170,11 @@ def measure_step65k(ctx, stream, steps, warmup):
             "fused": "rmsnorm(q,k) + rope2 + kv_rope2 + kv_copy | attention + merge + attn_gate16, per layer"}
 
 
-def measure_prefill(ctx, stream, steps, warmup):
+def measure_prefill(ctx, stream, steps, warmup, block=2048):
     import torch
     from mechta_b200 import kv
-    prefix, block = 32768, 2048
-    cache = kv.KvCache(ctx, kv.KvFormat.F16, N_LAYERS, prefix + block)
+    prefix = 32768
+    cache = kv.KvCache(ctx, kv.KvFormat.F16, N_LAYERS, (prefix + block + 1023) // 1024 * 1024)
     g = torch.Generator(device="cuda"); g.manual_seed(3)
     for p in range(0, prefix, 8192):  # the prefix, written once through the append kernel, then snapshotted
         k = torch.randn(N_LAYERS, 8192, 2, 256, device="cuda", generator=g)
