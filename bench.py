@@ -43,6 +43,17 @@ NCU_TRAFFIC_BYTES_DECODE65K = 138_800_000
 REGIONS = 5
 
 
+def decode65k_config(world: int) -> dict:
+    """`config` of the default line, the same for this repository's arm and for the reference arm."""
+    return {"workload": "decode65k", "layers": N_LAYERS, "context_tokens": 65536, "verify_tokens": 4, "cache": "f16",
+            "accept": "uniform 0..3 per step from a fixed seed",
+            "append": "the 4 new rows of all layers in one launch per step, then one attention launch per layer "
+                      "(other_workloads.step65k writes each layer's rows just before its attention)",
+            "parallelism": "single GPU" if world == 1 else
+                           f"{world} independent sessions of this shape, one per GPU, no collective on the data path",
+            "l2": "inputs larger than L2: every layer's K+V exceeds 126 MB and 9 other layers are read between reuses"}
+
+
 def measured_peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -188,8 +199,11 @@ def run_reference(args):
         "warmup": args.warmup, "ms_per_step": 1e3 * t / args.steps, "higher_is_better": True,
         "scaling": "weak" if workload == "decode65k" else "strong", "vs_baseline": None,
         "dtype": "f32 math over an %s cache" % ("f16" if fmt == 0 else "f32"), "data": "synthetic",
-        "config": {"workload": workload, "context_tokens": ctx_len, "layers": N_LAYERS, "verify_tokens": 4,
-                   "window_tokens": window, "note": "a step here is one layer-step of the sampled window"},
+        "config": decode65k_config(max(1, args.gpus)) if workload == "decode65k" else
+                  {"workload": workload, "context_tokens": ctx_len, "layers": N_LAYERS, "verify_tokens": 4, "cache": "f32"},
+        "reference_sample": {"window_tokens": window, "context_tokens": ctx_len,
+                             "note": "a step of this arm is one layer-step (1 of the 10 layers) over the sampled window, on the "
+                                     "host cores of one process whatever --gpus says"},
         "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -449,14 +463,9 @@ def run_decode65k(args):
                 "metric": "kv_read_gbps", "value": value, "unit": "GB/s", "n_gpus": world, "steps": steps, "warmup": warmup,
                 "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-                "config": {"workload": "decode65k", "layers": N_LAYERS, "context_tokens": ctx0, "verify_tokens": 4,
-                           "cache": "f16", "accept": "uniform 0..3 per step from a fixed seed", "capacity_tokens": context,
-                           "append": "the 4 new rows of all layers in one launch per step, then one attention launch per layer "
-                                     "(other_workloads.step65k writes each layer's rows just before its attention)",
-                           "parallelism": "single GPU" if world == 1 else
-                                          f"{world} independent sessions of this shape, one per GPU, no collective on the data path",
-                           "l2": "inputs larger than L2: every layer's K+V exceeds 126 MB and 9 other layers are read between reuses",
-                           "hbm_frac_of_8TBps_nominal": value / 8000.0 / world},
+                "config": decode65k_config(world),
+                "capacity_tokens": context,
+                "hbm_frac_of_8TBps_nominal": value / 8000.0 / world,
                 "repeats": {"regions": REGIONS, "ms_per_step": rep,
                             "note": "the K timed steps run `regions` times from the same starting state; "
                                     "ms_per_step and value are the median region, max over ranks per region"},
@@ -529,7 +538,7 @@ def cpu_baseline(workload, fmt, ctx0, per_pos):
     kc, vc = host_cache(oracle, fmt, ctx0 + 64, 7)
     pos, t, n, nbytes = ctx0, 0.0, 0, 0
     cpu_layer_step(oracle, fmt, kc, vc, pos, 7, 0)  # warm
-    while t < 10.0 and n < 40:
+    while t < 10.0 and n < 400:
         t += cpu_layer_step(oracle, fmt, kc, vc, pos, 7, n + 1)
         nbytes += (pos + 4) * per_pos
         pos += 1
