@@ -1,4 +1,5 @@
-"""Generates tests/golden/config0.npz: known answers for the CPU-runnable configuration (BASELINE.json configs[0]),
+"""Generates tests/golden/config0.npz: known answers for the CPU-runnable configuration (one full-attention layer, f16
+cache of 4,096 prior tokens, a 4-token verify step with append and rollback),
 and tests/golden/step.npz: the fused layer step and the ring / window / sinks variant on the same prior cache.
 
 The reference cannot run where this was written (Rust + wgpu/Vulkan; no graphics stack), and it holds no fixture
