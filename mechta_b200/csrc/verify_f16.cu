@@ -480,11 +480,12 @@ static bool verify_use_tc() {
     }();
     return tc;
 }
-// MKV_VERIFY32=tc selects the tcgen05 kernel for the f32 cache; the default is the warp-MMA kernel of verify_f32.cu.
+// The f32 cache runs on the tcgen05 kernel of verify_f32_tc.cu; MKV_VERIFY32=mma selects the warp-MMA kernel of
+// verify_f32.cu (kept for comparison).
 static bool verify32_use_tc() {
     static const bool tc = [] {
         const char *e = getenv("MKV_VERIFY32");
-        return e && strcmp(e, "tc") == 0;
+        return !(e && strcmp(e, "mma") == 0);
     }();
     return tc;
 }
