@@ -112,7 +112,7 @@ def measure_verify262k(ctx, stream, fmt, layers=2, steps=12, warmup=3):
     cache.close()
     return {"workload": f"verify262k_{fmt.name.lower()}", "context_tokens": n, "layers": layers, "steps": steps,
             "us_per_launch": 1e3 * ms / (steps * layers), "value": gbs, "unit": "GB/s", "frac": gbs / hbm, "peak": hbm,
-            "peak_kind": kind, "kernel": "verify_f16_tc_kernel" if fmt == kv.KvFormat.F16 else "verify_f32_kernel",
+            "peak_kind": kind, "kernel": "verify_f16_tc_kernel" if fmt == kv.KvFormat.F16 else "verify_f32_tc_kernel",
             "note": "whole loop: one append launch per step + the attention launches, inputs resident"}
 
 

@@ -37,6 +37,15 @@ namespace mkv {
 using namespace ptx;
 
 constexpr int FT_NSLOT = 5;
+#ifndef FT_CONV_UNROLL
+#define FT_CONV_UNROLL 2
+#endif
+#ifdef FT_X_NOMMA
+#define FT_X_MMA(x) do { (void)a; } while (0)
+#else
+#define FT_X_MMA(x) x
+#endif
+constexpr int FT_CONV_UNROLL_N = FT_CONV_UNROLL; // half rows a converter lane has in flight
 constexpr int FT_THREADS = 512;
 constexpr uint32_t FT_SOFTMAX_TID0 = 384;
 constexpr uint32_t FT_TILE = 128;                     // keys per tile
@@ -68,6 +77,18 @@ struct FtShared {
     volatile uint32_t abort;
     uint32_t ticket;
 };
+
+// Measurement build only: cycles each role spent waiting, summed over the CTAs of all launches since the last read.
+#ifdef MKV_MEASURE
+enum { FP_CTAS, FP_TOTAL, FP_PDL, FP_PROD_EMPTY, FP_MMA_IDLE, FP_MMA_Q, FP_CONV_FULL, FP_SM_S, FP_SM_O, FP_SM_PDL, FP_FIRST_S,
+       FP_MERGE, FP_N };
+__device__ unsigned long long g_ft_probe[16];
+#define FT_PROBE_BEGIN(cond) long long fp_t0 = 0; if (cond) fp_t0 = clock64()
+#define FT_PROBE_END(cond, which) do { if (cond) atomicAdd(&g_ft_probe[which], (unsigned long long)(clock64() - fp_t0)); } while (0)
+#else
+#define FT_PROBE_BEGIN(cond) do { } while (0)
+#define FT_PROBE_END(cond, which) do { } while (0)
+#endif
 
 __device__ __forceinline__ bool ft_wait(uint32_t bar, uint32_t parity, FtShared *sh, uint32_t *status) {
     if (sh->abort) return false;
@@ -137,6 +158,9 @@ verify_f32_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
     const uint32_t local = blockIdx.x - it.cta_begin;
     if (local >= 2u * it.nsplit) return;
     pdl_launch_dependents();
+#ifdef MKV_MEASURE
+    const long long fp_start = clock64();
+#endif
     const uint32_t kvh = local & 1u, split = local >> 1;
     const uint32_t t0 = it.tile_begin + split * it.tiles_per_split; // in 32-key units
     const uint32_t t1 = min(t0 + it.tiles_per_split, it.tile_end);
@@ -199,10 +223,14 @@ verify_f32_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
                 const uint32_t key0 = k_begin + tile * FT_TILE;
                 // tiles wholly below safe_below hold rows no kernel still in flight writes: their loads start at once
                 if (!waited && key0 + FT_TILE > it.safe_below) {
+                    FT_PROBE_BEGIN(true);
                     pdl_wait();
+                    FT_PROBE_END(true, FP_PDL);
                     waited = true;
                 }
+                FT_PROBE_BEGIN(true);
                 if (n >= (uint32_t)FT_NSLOT && !ft_wait(bar_empty + 8u * slot, ((n / FT_NSLOT) - 1u) & 1u, sh, status)) break;
+                FT_PROBE_END(true, FP_PROD_EMPTY);
                 const uint32_t bar = bar_full + 8u * slot, dst = smem_base + slot * FT_SLOT;
                 const CUtensorMap *map = is_v ? vmap : kmap;
                 const int x = (int)(kvh * 256u + sub * 64u);
@@ -222,7 +250,9 @@ verify_f32_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
             constexpr uint32_t IDESC_QK32 = tc_idesc_f16(128, 32, false, false);
             constexpr uint32_t IDESC_PV = tc_idesc_f16(128, 64, false, true);
             const uint32_t qb = smem_base + FT_OFF_Q, pb = smem_base + FT_OFF_P;
+            FT_PROBE_BEGIN(true);
             bool ok = ft_wait(bar_q_full, 0, sh, status);
+            FT_PROBE_END(true, FP_MMA_Q);
             tc_fence_after();
             // Event loop over sub-tiles: whichever of "the next K sub-tile is converted (and its S^T buffer is free)"
             // and "the next V sub-tile is converted, its P^T written and O_t^T free" holds first is issued first.
@@ -252,7 +282,7 @@ verify_f32_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
                                 const uint32_t dim = 64u * p + 32u * b + 16u * (s >> 1); // first of the 16 dims
                                 const uint64_t a = tc_desc_sw128(kb + b * FT_BLK + s * 32u, 16, 1024);
                                 const uint64_t q = tc_desc_sw128(qb + (dim >> 6) * FT_QB + (dim & 63u) * 2u, 16, 1024);
-                                tc_mma_f16(d, a, q, (s & 1u) ? IDESC_QK32 : IDESC_QK64, (p | b | s) ? 1u : 0u);
+                                FT_X_MMA(tc_mma_f16(d, a, q, (s & 1u) ? IDESC_QK32 : IDESC_QK64, (p | b | s) ? 1u : 0u));
                             }
                         tc_commit(bar_empty + 8u * slot); // the sub-tile's slot is free
                         if (p == 3u) tc_commit(bar_s_full + 8u * (j & 1u));
@@ -275,7 +305,7 @@ verify_f32_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
                             // V'^T, M-major: the second block of 32 dims one block on, the next 8 keys 1024 bytes on
                             const uint64_t a = tc_desc_sw128(vb + ks * 2048u, FT_BLK, 1024);
                             const uint64_t b = tc_desc_sw128(pbj + (ks >> 2) * FT_PB + (ks & 3u) * 32u, 16, 1024);
-                            tc_mma_f16(tmem + FT_COL_O + 64u * p, a, b, IDESC_PV, ks ? 1u : 0u);
+                            FT_X_MMA(tc_mma_f16(tmem + FT_COL_O + 64u * p, a, b, IDESC_PV, ks ? 1u : 0u));
                         }
                         tc_commit(bar_empty + 8u * slot);
                         if (p == 3u) tc_commit(bar_o_full); // O_t^T of tile j is complete; P^T buffer j & 1 may be overwritten
@@ -284,6 +314,9 @@ verify_f32_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
                     }
                 }
                 if (did) {
+#ifdef MKV_MEASURE
+                    atomicAdd(&g_ft_probe[FP_MMA_IDLE], (unsigned long long)(clock64() - tlast));
+#endif
                     tlast = clock64();
                 } else if (sh->abort || clock64() - tlast > FT_WAIT_LIMIT) {
                     if (!sh->abort) {
@@ -305,10 +338,13 @@ verify_f32_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
         for (uint32_t n = 0; n < nsub; n++) {
             if (((n % FT_NSLOT) & 3u) != c) continue; // slots 0..3 -> pairs 0..3, slot 4 -> pair 0
             const uint32_t slot = n % FT_NSLOT;
+            FT_PROBE_BEGIN(tid == 128u);
             if (!__all_sync(0xffffffffu, ft_wait(bar_full + 8u * slot, (n / FT_NSLOT) & 1u, sh, status))) break;
+            FT_PROBE_END(tid == 128u, FP_CONV_FULL);
             uint8_t *base = smem + slot * FT_SLOT;
             // 256 half rows of 64 bytes in this warp's block; a lane takes half row (row = i * 16 + lane / 2, half = lane % 2)
-#pragma unroll 2
+#ifndef FT_X_NOCONV
+#pragma unroll FT_CONV_UNROLL_N
             for (uint32_t i = 0; i < 8u; i++) {
                 const uint32_t row = i * 16u + (lane >> 1), half = lane & 1u;
                 uint8_t *r = base + blk * FT_BLK + row * 128u;
@@ -324,6 +360,7 @@ verify_f32_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
                 *reinterpret_cast<uint4 *>(r + (((c0 + 2u) ^ x) << 4)) = l0;
                 *reinterpret_cast<uint4 *>(r + (((c0 + 3u) ^ x) << 4)) = l1;
             }
+#endif
             fence_proxy_async(); // the tensor core reads the tile through the async proxy
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_conv + 8u * slot);
@@ -335,7 +372,11 @@ verify_f32_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
         // ---------------- softmax: one thread per key of the tile (TMEM lane); owners of O ----------------
         const uint32_t w4 = warp & 3u; // the warp's TMEM lane group
         const uint32_t klane = 32u * w4 + lane, lane_addr = (32u * w4) << 16;
-        pdl_wait(); // Q and every global write come after this
+        {
+            FT_PROBE_BEGIN(tid == FT_SOFTMAX_TID0);
+            pdl_wait(); // Q and every global write come after this
+            FT_PROBE_END(tid == FT_SOFTMAX_TID0, FP_SM_PDL);
+        }
         // Q of this KV head to shared memory as f16 hi (rows 0-31) and lo (rows 32-63), the B operands of S^T:
         // row = tok * 8 + head % 8 (the order of q_dmx, M/dmx.rs:128-138), rows of tokens >= ntok zero; per 64-dim block
         // [64 rows][128 bytes], 128-byte swizzle. All loads of a thread go out before the first conversion.
@@ -397,7 +438,9 @@ verify_f32_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
         bool stopped = false;
         uint32_t folded = 0; // tiles whose O_t^T has been folded into O
         auto fold = [&](uint32_t j) -> bool { // O = O + O_t^T of tile j (the rescale for a moved maximum was applied before)
+            FT_PROBE_BEGIN(tid == FT_SOFTMAX_TID0);
             bool ok = __all_sync(0xffffffffu, ft_wait(bar_o_full, j & 1u, sh, status));
+            FT_PROBE_END(tid == FT_SOFTMAX_TID0, FP_SM_O);
             tc_fence_after();
             if (ok) {
 #pragma unroll
@@ -424,7 +467,12 @@ verify_f32_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
         };
         for (uint32_t j = 0; j < nt; j++) {
             // a warp takes every wait's outcome together: the TMEM loads are warp-collective
+            FT_PROBE_BEGIN(tid == FT_SOFTMAX_TID0);
             bool ok = __all_sync(0xffffffffu, ft_wait(bar_s_full + 8u * (j & 1u), (j >> 1) & 1u, sh, status));
+            FT_PROBE_END(tid == FT_SOFTMAX_TID0, FP_SM_S);
+#ifdef MKV_MEASURE
+            if (tid == FT_SOFTMAX_TID0 && j == 0u) atomicAdd(&g_ft_probe[FP_FIRST_S], (unsigned long long)(clock64() - fp_start));
+#endif
             tc_fence_after();
             float t[32];
             {
@@ -589,8 +637,28 @@ verify_f32_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
         tmem_dealloc(tmem, FT_COLS);
     }
     // this CTA's share of the merge, if its ticket gives it one (scratch in the ring, which is drained by now)
+#ifdef MKV_MEASURE
+    const long long fp_merge = clock64();
+#endif
     finish_item<FT_THREADS, EXT>(it, *reinterpret_cast<FinishSmem *>(smem), status, sh->ticket);
+#ifdef MKV_MEASURE
+    if (tid == 0) {
+        const long long now = clock64();
+        atomicAdd(&g_ft_probe[FP_CTAS], 1ull);
+        atomicAdd(&g_ft_probe[FP_TOTAL], (unsigned long long)(now - fp_start));
+        atomicAdd(&g_ft_probe[FP_MERGE], (unsigned long long)(now - fp_merge));
+    }
+#endif
 }
+
+#ifdef MKV_MEASURE
+// Measurement build only: copies the 16 role counters of verify_f32_tc_kernel to `out16` and clears them.
+extern "C" int mkv_measure_f32_roles(unsigned long long *out16) {
+    if (cudaMemcpyFromSymbol(out16, g_ft_probe, sizeof g_ft_probe) != cudaSuccess) return 1;
+    const unsigned long long zero[16] = {};
+    return cudaMemcpyToSymbol(g_ft_probe, zero, sizeof zero) != cudaSuccess;
+}
+#endif
 
 mkv_status verify_f32_tc_setup_device() {
     MKV_CUDA(cudaFuncSetAttribute(verify_f32_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FT_SMEM));
