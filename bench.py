@@ -535,10 +535,11 @@ def cpu_baseline(workload, fmt, ctx0, per_pos):
     from oracle import oracle
     oracle.build()
     cores = oracle.use_all_cores()
-    kc, vc = host_cache(oracle, fmt, ctx0 + 64, 7)
+    max_steps = 400
+    kc, vc = host_cache(oracle, fmt, ctx0 + max_steps + 8, 7)  # every step moves on one position and appends 4 rows
     pos, t, n, nbytes = ctx0, 0.0, 0, 0
     cpu_layer_step(oracle, fmt, kc, vc, pos, 7, 0)  # warm
-    while t < 10.0 and n < 400:
+    while t < 10.0 and n < max_steps:
         t += cpu_layer_step(oracle, fmt, kc, vc, pos, 7, n + 1)
         nbytes += (pos + 4) * per_pos
         pos += 1

@@ -380,7 +380,7 @@ def measure_longctx(ctx, stream, world, rank, local, group, steps, warmup, excha
     hbm, _, kind = peaks()
     res = {"workload": "longctx", "value": value, "unit": "GB/s", "n_gpus": world, "steps": steps, "ms_per_step": ms / steps,
            "ms_per_step_spread": sp, "scaling": "strong", "context_tokens": ctx0, "cache": "f32", "layers": N_LAYERS,
-           "kernel": "verify_f32_kernel", "frac_per_gpu": value / world / hbm, "peak": hbm, "peak_kind": kind,
+           "kernel": "verify_f32_tc_kernel", "frac_per_gpu": value / world / hbm, "peak": hbm, "peak_kind": kind,
            "exchange": ("none (one GPU)" if world == 1 else
                         "rows of the record pushed peer to peer over NVLink and merged by the attention kernel's own CTAs"
                         if exchange == "p2p" else "NCCL all-gather of records + merge kernel"),

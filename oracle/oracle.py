@@ -100,6 +100,8 @@ def append(fmt, kc, vc, pos, k, v, tab):
     """k = [ntok][2][256] f32, v = [ntok][2][256] f32, tab = [ntok][64] f32 or None."""
     k = np.ascontiguousarray(k, np.float32); v = np.ascontiguousarray(v, np.float32)
     ntok = k.shape[0]
+    if pos < 0 or pos + ntok > kc.shape[0] or pos + ntok > vc.shape[0]:
+        raise ValueError(f"rows [{pos}, {pos + ntok}) do not fit a cache of {min(kc.shape[0], vc.shape[0])} rows")
     t = None if tab is None else _p(np.ascontiguousarray(tab, np.float32))
     lib().mko_append_k(fmt, _p(kc), pos, ntok, _p(k), t)
     lib().mko_append_v(fmt, _p(vc), pos, ntok, _p(v))
