@@ -40,10 +40,15 @@ constexpr int FT_NSLOT = 5;
 #ifndef FT_CONV_UNROLL
 #define FT_CONV_UNROLL 2
 #endif
-#ifdef FT_X_NOMMA
-#define FT_X_MMA(x) do { (void)a; } while (0)
+#if defined(FT_X_NOMMA) || defined(FT_X_NOQK)
+#define FT_X_QK(x) do { (void)a; } while (0)
 #else
-#define FT_X_MMA(x) x
+#define FT_X_QK(x) x
+#endif
+#if defined(FT_X_NOMMA) || defined(FT_X_NOPV)
+#define FT_X_PV(x) do { (void)a; } while (0)
+#else
+#define FT_X_PV(x) x
 #endif
 constexpr int FT_CONV_UNROLL_N = FT_CONV_UNROLL; // half rows a converter lane has in flight
 constexpr int FT_THREADS = 512;
@@ -282,7 +287,7 @@ verify_f32_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
                                 const uint32_t dim = 64u * p + 32u * b + 16u * (s >> 1); // first of the 16 dims
                                 const uint64_t a = tc_desc_sw128(kb + b * FT_BLK + s * 32u, 16, 1024);
                                 const uint64_t q = tc_desc_sw128(qb + (dim >> 6) * FT_QB + (dim & 63u) * 2u, 16, 1024);
-                                FT_X_MMA(tc_mma_f16(d, a, q, (s & 1u) ? IDESC_QK32 : IDESC_QK64, (p | b | s) ? 1u : 0u));
+                                FT_X_QK(tc_mma_f16(d, a, q, (s & 1u) ? IDESC_QK32 : IDESC_QK64, (p | b | s) ? 1u : 0u));
                             }
                         tc_commit(bar_empty + 8u * slot); // the sub-tile's slot is free
                         if (p == 3u) tc_commit(bar_s_full + 8u * (j & 1u));
@@ -305,7 +310,7 @@ verify_f32_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
                             // V'^T, M-major: the second block of 32 dims one block on, the next 8 keys 1024 bytes on
                             const uint64_t a = tc_desc_sw128(vb + ks * 2048u, FT_BLK, 1024);
                             const uint64_t b = tc_desc_sw128(pbj + (ks >> 2) * FT_PB + (ks & 3u) * 32u, 16, 1024);
-                            FT_X_MMA(tc_mma_f16(tmem + FT_COL_O + 64u * p, a, b, IDESC_PV, ks ? 1u : 0u));
+                            FT_X_PV(tc_mma_f16(tmem + FT_COL_O + 64u * p, a, b, IDESC_PV, ks ? 1u : 0u));
                         }
                         tc_commit(bar_empty + 8u * slot);
                         if (p == 3u) tc_commit(bar_o_full); // O_t^T of tile j is complete; P^T buffer j & 1 may be overwritten
