@@ -121,6 +121,10 @@ __device__ __forceinline__ void merge_row(const VerifyItem &it, uint32_t r, Fini
     const float4 *po = reinterpret_cast<const float4 *>(it.part_o + ((size_t)kvh * ns * 32u + row) * 256u) + c4;
     float4 x[RND];
     float m = NEG_BIG, l = 0.0f;
+    // the head's gate values, if any, with the first loads: at the end of the row they would be one more round trip
+    float4 gate = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (!it.partial && it.gate && tid < FIN_COLS)
+        gate = __ldg(reinterpret_cast<const float4 *>(it.gate + ((size_t)tok * 16u + head) * 512u + 256u + 4 * tid));
     if (tid < ns) { // (m, l) first: the maximum is needed before anything can be summed
         const float2 y = __ldcg(ml + (size_t)tid * 32u);
         m = y.x;
@@ -204,7 +208,7 @@ __device__ __forceinline__ void merge_row(const VerifyItem &it, uint32_t r, Fini
             float4 y = make_float4(a.x * inv, a.y * inv, a.z * inv, a.w * inv);
             const size_t o = (size_t)tok * 4096u + (size_t)head * 256u + 4 * tid;
             if (it.gate) { // attn_gate of the reference (W/ops.wgsl:171-177): times the sigmoid of the head's gate values
-                const float4 g = *reinterpret_cast<const float4 *>(it.gate + ((size_t)tok * 16u + head) * 512u + 256u + 4 * tid);
+                const float4 g = gate;
                 y.x *= 1.0f / (1.0f + expf(-g.x));
                 y.y *= 1.0f / (1.0f + expf(-g.y));
                 y.z *= 1.0f / (1.0f + expf(-g.z));
