@@ -23,8 +23,8 @@
 // kept in registers with a rounded FMA, O = O * cf + O_t (64 values per thread), which also makes the rescale after
 // a move of the reference maxima a register operation.
 // Roles (512 threads, four warpgroups whose register budgets are set with setmaxnreg): warp 0 = TMA producer, warp 1 = MMA
-// issuer and TMEM owner (warps 2-3 idle), warps 4-11 = converters (two warps per sub-tile, one block each; a ring slot
-// always goes to the same pair, so each slot's barrier phases are consumed in order), warps 12-15 = softmax (one thread
+// issuer and TMEM owner (warps 2-3 idle), warps 4-11 = converters (four warps per sub-tile, 64 keys of one block each; a ring
+// slot always goes to the same four, so each slot's barrier phases are consumed in order), warps 12-15 = softmax (one thread
 // per key of the tile) and owners of O. Stream order K0 K1 V0 K2 V1 ... in sub-tiles of four per K or V tile.
 // Same pieces, in-kernel merge and programmatic dependent launch as the f16 kernel; every wait is bounded.
 #include <stdlib.h>
@@ -50,6 +50,7 @@ constexpr int FT_NSLOT = 5;
 #else
 #define FT_X_PV(x) x
 #endif
+constexpr uint32_t FT_CONV_ITERS = 4, FT_CONV_WARPS = 4; // a sub-tile is converted by four warps: 64 keys of one block each
 constexpr int FT_CONV_UNROLL_N = FT_CONV_UNROLL; // half rows a converter lane has in flight
 constexpr int FT_THREADS = 512;
 constexpr uint32_t FT_SOFTMAX_TID0 = 384;
@@ -195,7 +196,7 @@ verify_f32_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
     if (tid == 0) {
         for (int i = 0; i < FT_NSLOT; i++) {
             mbar_init(bar_full + 8u * i, 1);
-            mbar_init(bar_conv + 8u * i, 2);
+            mbar_init(bar_conv + 8u * i, FT_CONV_WARPS);
             mbar_init(bar_empty + 8u * i, 1);
         }
         for (int i = 0; i < 2; i++) {
@@ -338,20 +339,21 @@ verify_f32_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
     } else if (warp < 12) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
         // ---------------- converters: f32 sub-tile -> f16 hi / lo operand tile, in place ----------------
-        // Every use of a ring slot is converted by the same warp, in order.
-        const uint32_t c = (warp - 4u) >> 1, blk = warp & 1u;
+        // Every use of a ring slot is converted by the same four warps, in order (a barrier's phases must be waited for in
+        // order by whoever waits on it).
+        const uint32_t c = (warp - 4u) >> 2, blk = warp & 1u, rbase = 64u * ((warp >> 1) & 1u);
         for (uint32_t n = 0; n < nsub; n++) {
-            if (((n % FT_NSLOT) & 3u) != c) continue; // slots 0..3 -> pairs 0..3, slot 4 -> pair 0
+            if (((n % FT_NSLOT) & 1u) != c) continue; // slots 0, 2, 4 -> the first four warps, 1, 3 -> the other four
             const uint32_t slot = n % FT_NSLOT;
             FT_PROBE_BEGIN(tid == 128u);
             if (!__all_sync(0xffffffffu, ft_wait(bar_full + 8u * slot, (n / FT_NSLOT) & 1u, sh, status))) break;
             FT_PROBE_END(tid == 128u, FP_CONV_FULL);
             uint8_t *base = smem + slot * FT_SLOT;
-            // 256 half rows of 64 bytes in this warp's block; a lane takes half row (row = i * 16 + lane / 2, half = lane % 2)
+            // 128 half rows of 64 bytes for this warp; a lane takes half row (row = rbase + i * 16 + lane / 2, half = lane % 2)
 #ifndef FT_X_NOCONV
 #pragma unroll FT_CONV_UNROLL_N
-            for (uint32_t i = 0; i < 8u; i++) {
-                const uint32_t row = i * 16u + (lane >> 1), half = lane & 1u;
+            for (uint32_t i = 0; i < FT_CONV_ITERS; i++) {
+                const uint32_t row = rbase + i * 16u + (lane >> 1), half = lane & 1u;
                 uint8_t *r = base + blk * FT_BLK + row * 128u;
                 const uint32_t x = row & 7u, c0 = 4u * half;
                 float4 f[4];
