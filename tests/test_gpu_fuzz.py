@@ -69,13 +69,13 @@ def test_random_steps_against_the_oracle(oracle, seed):
     ctx.close()
 
 
-def test_f32_cache_on_the_tcgen05_kernel_in_a_child_process():
-    """MKV_VERIFY32=tc selects the tcgen05 kernel for the f32 cache (read once per process, so a child process runs
-    the same random steps with it)."""
+def test_f32_cache_on_the_warp_mma_kernel_in_a_child_process():
+    """The f32 cache runs on the tcgen05 kernel; MKV_VERIFY32=mma selects the warp-MMA kernel kept as the measured
+    baseline (read once per process, so a child process runs the same random steps with it)."""
     import os
     import subprocess
     import sys
-    env = dict(os.environ, MKV_VERIFY32="tc")
+    env = dict(os.environ, MKV_VERIFY32="mma")
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     r = subprocess.run([sys.executable, "-m", "pytest", os.path.join(root, "tests", "test_gpu_fuzz.py"), "-q", "-x", "-m", "gpu", "-k",
                         "random_steps"], env=env, cwd=root, capture_output=True, text=True, timeout=600)
