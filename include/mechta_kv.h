@@ -261,6 +261,17 @@ mkv_status mkv_restore(mkv_cache *c, uint32_t p, const void *src_host, size_t by
 mkv_status mkv_host_alloc(size_t bytes, void **out);
 void mkv_host_free(void *p);
 
+/* ---- the checked build (make -C mechta_b200/csrc checks: libmechta_kv_checks.so, -DMKV_CHECKS). The reference relies
+ * on wgpu's bounds checks on every buffer access (engine/crates/shader/src/lib.rs:13-22 keeps them on); here every
+ * buffer of a cache (K and V rows of each layer, the split-K pieces) is allocated between two 64 KB runs of a canary
+ * byte, and mkv_cache_check_guards counts the canary bytes that changed (blocks on the context's streams).
+ * mkv_checks_enabled: 1 in the checked build, 0 in the shipped one, whose check finds nothing to look at and reports 0.
+ * mkv_checks_touch_guard: checked build only, for the test of the check itself: overwrites three canary bytes from
+ * the host side (a cudaMemset inside the library's own allocation). */
+int mkv_checks_enabled(void);
+mkv_status mkv_cache_check_guards(mkv_cache *c, uint64_t *bad_bytes);
+mkv_status mkv_checks_touch_guard(mkv_cache *c);
+
 /* ---- root files: the KV section of the reference's on-disk prefix cache, "MECHTA-ROOT-1\n"
  * (M/session.rs:92-129): u64 p, u64 n_ssm, u64 n_kv, p x u32 tokens, then length-prefixed f32-word vectors
  * ssm.., conv.., (K, V)... Files written here carry n_ssm = 0; files with DeltaNet states are read and the

@@ -49,6 +49,14 @@ def build(force: bool = False) -> str:
     return SO_PATH
 
 
+def build_checks() -> str:
+    """Compile the checked build (every cache buffer between canary bytes): libmechta_kv_checks.so beside the library."""
+    r = subprocess.run(["make", "-C", os.path.join(_HERE, "csrc"), "checks"], capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("building libmechta_kv_checks.so failed:\n" + r.stdout[-4000:] + r.stderr[-4000:])
+    return os.path.join(_HERE, "libmechta_kv_checks.so")
+
+
 _SIGS = {
     # name: (restype, argtypes)
     "mkv_strerror": (C.c_char_p, [C.c_int]),
@@ -62,6 +70,9 @@ _SIGS = {
     "mkv_prof_read": (C.c_int, [C.c_void_p, C.POINTER(C.c_double), C.POINTER(C.c_uint64)]),
     "mkv_cache_create": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(C.c_void_p)]),
     "mkv_cache_destroy": (None, [C.c_void_p]),
+    "mkv_checks_enabled": (C.c_int, []),
+    "mkv_cache_check_guards": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint64)]),
+    "mkv_checks_touch_guard": (C.c_int, [C.c_void_p]),
     "mkv_cache_buffers": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)]),
     "mkv_cache_len": (C.c_uint32, [C.c_void_p]),
     "mkv_cache_set_len": (C.c_int, [C.c_void_p, C.c_uint32]),

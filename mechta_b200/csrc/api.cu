@@ -117,17 +117,57 @@ static mkv_status check_device_status(Ctx *ctx) {
     return MKV_OK;
 }
 
+// ---- guarded allocations (the checked build, -DMKV_CHECKS) ---------------------------------------------------
+// Every buffer of a cache (the K and V rows of each layer, the split-K pieces) is bracketed by GUARD bytes of a canary
+// pattern that no kernel may touch; mkv_cache_check_guards counts the bytes that changed. The shipped build allocates
+// the buffers as they are and its check has nothing to look at.
+#ifdef MKV_CHECKS
+static constexpr size_t GUARD = 65536; // a multiple of every alignment the kernels and TMA ask of a buffer
+static constexpr int CANARY = 0xA5;
+#else
+static constexpr size_t GUARD = 0;
+#endif
+static cudaError_t guard_malloc(Cache *c, void **out, size_t bytes) {
+    char *p = nullptr;
+    cudaError_t e = cudaMalloc(reinterpret_cast<void **>(&p), bytes + 2 * GUARD);
+    if (e != cudaSuccess) return e;
+#ifdef MKV_CHECKS
+    if ((e = cudaMemset(p, CANARY, GUARD)) != cudaSuccess || (e = cudaMemset(p + GUARD + bytes, CANARY, GUARD)) != cudaSuccess) {
+        cudaFree(p);
+        return e;
+    }
+    c->guarded.push_back({p + GUARD, bytes});
+#else
+    (void)c;
+#endif
+    *out = p + GUARD;
+    return cudaSuccess;
+}
+static void guard_free(Cache *c, void *p) {
+    if (!p) return;
+#ifdef MKV_CHECKS
+    for (size_t i = 0; i < c->guarded.size(); i++)
+        if (c->guarded[i].first == p) {
+            c->guarded.erase(c->guarded.begin() + (long)i);
+            break;
+        }
+#else
+    (void)c;
+#endif
+    cudaFree(static_cast<char *>(p) - GUARD);
+}
+
 static mkv_status ensure_scratch(Cache *c, size_t pieces) {
     if (pieces <= c->scratch_pieces) return MKV_OK;
     Ctx *ctx = c->ctx;
     // earlier launches may still read the old buffers
     MKV_CUDA(cudaStreamSynchronize(ctx->stream));
-    if (c->part_ml) cudaFree(c->part_ml);
-    if (c->part_o) cudaFree(c->part_o);
+    guard_free(c, c->part_ml);
+    guard_free(c, c->part_o);
     c->part_ml = c->part_o = nullptr;
     c->scratch_pieces = 0;
-    if (cudaMalloc(&c->part_ml, pieces * 32 * 2 * sizeof(float)) != cudaSuccess ||
-        cudaMalloc(&c->part_o, pieces * 32 * 256 * sizeof(float)) != cudaSuccess) {
+    if (guard_malloc(c, reinterpret_cast<void **>(&c->part_ml), pieces * 32 * 2 * sizeof(float)) != cudaSuccess ||
+        guard_malloc(c, reinterpret_cast<void **>(&c->part_o), pieces * 32 * 256 * sizeof(float)) != cudaSuccess) {
         cudaGetLastError();
         set_error("out of device memory for %zu split-K pieces", pieces);
         return MKV_ERR_NOMEM;
@@ -485,7 +525,7 @@ static mkv_status cache_create_common(mkv_ctx *h, mkv_fmt fmt, int n_layers, uin
         return s;
     };
     for (int l = 0; l < n_layers; l++) {
-        if (cudaMalloc(&c->k[l], c->buf_bytes) != cudaSuccess || cudaMalloc(&c->v[l], c->buf_bytes) != cudaSuccess) {
+        if (guard_malloc(c, &c->k[l], c->buf_bytes) != cudaSuccess || guard_malloc(c, &c->v[l], c->buf_bytes) != cudaSuccess) {
             cudaGetLastError();
             set_error("out of device memory for layer %d of %d (%zu bytes per buffer)", l, n_layers, c->buf_bytes);
             return fail(MKV_ERR_NOMEM);
@@ -544,21 +584,68 @@ mkv_status mkv_cache_create_ring(mkv_ctx *h, mkv_fmt fmt, int n_layers, uint32_t
     return cache_create_common(h, fmt, n_layers, context, 0, 0, ring_rows, out);
 }
 
+int mkv_checks_enabled(void) {
+#ifdef MKV_CHECKS
+    return 1;
+#else
+    return 0;
+#endif
+}
+
+mkv_status mkv_cache_check_guards(mkv_cache *h, uint64_t *bad_bytes) {
+    Cache *c = reinterpret_cast<Cache *>(h);
+    if (!c || !bad_bytes) {
+        set_error("null cache or result pointer");
+        return MKV_ERR_INVALID;
+    }
+    *bad_bytes = 0;
+#ifdef MKV_CHECKS
+    mkv_status st = use_device(c->ctx);
+    if (st != MKV_OK) return st;
+    MKV_CUDA(cudaStreamSynchronize(c->ctx->stream));
+    MKV_CUDA(cudaStreamSynchronize(c->ctx->copy_stream));
+    std::vector<unsigned char> host(2 * GUARD);
+    for (const auto &g : c->guarded) {
+        char *p = static_cast<char *>(g.first);
+        MKV_CUDA(cudaMemcpy(host.data(), p - GUARD, GUARD, cudaMemcpyDeviceToHost));
+        MKV_CUDA(cudaMemcpy(host.data() + GUARD, p + g.second, GUARD, cudaMemcpyDeviceToHost));
+        for (unsigned char b : host) *bad_bytes += b != CANARY;
+    }
+#endif
+    return MKV_OK;
+}
+
+mkv_status mkv_checks_touch_guard(mkv_cache *h) {
+#ifdef MKV_CHECKS
+    Cache *c = reinterpret_cast<Cache *>(h);
+    if (!c || c->guarded.empty()) {
+        set_error("no guarded buffer");
+        return MKV_ERR_INVALID;
+    }
+    mkv_status st = use_device(c->ctx);
+    if (st != MKV_OK) return st;
+    MKV_CUDA(cudaMemset(static_cast<char *>(c->guarded[0].first) + c->guarded[0].second + 7, 0, 3));
+    return MKV_OK;
+#else
+    (void)h;
+    set_error("not a checked build");
+    return MKV_ERR_UNSUPPORTED;
+#endif
+}
+
 void mkv_cache_destroy(mkv_cache *h) {
     Cache *c = reinterpret_cast<Cache *>(h);
     if (!c) return;
     cudaSetDevice(c->ctx->device);
     cudaStreamSynchronize(c->ctx->stream);
     cudaStreamSynchronize(c->ctx->copy_stream);
-    for (void *p : c->k)
-        if (p) cudaFree(p);
-    for (void *p : c->v)
-        if (p) cudaFree(p);
+    for (void *p : c->k) guard_free(c, p);
+    for (void *p : c->v) guard_free(c, p);
     if (c->maps_dev) cudaFree(c->maps_dev);
     if (c->kptrs_dev) cudaFree(c->kptrs_dev);
     if (c->vptrs_dev) cudaFree(c->vptrs_dev);
-    if (c->part_ml) cudaFree(c->part_ml);
-    if (c->part_o) cudaFree(c->part_o);
+    guard_free(c, c->part_ml);
+    guard_free(c, c->part_o);
     if (c->qr) cudaFree(c->qr);
     if (c->ev_snapshot) cudaEventDestroy(c->ev_snapshot);
     Ctx *ctx = c->ctx;

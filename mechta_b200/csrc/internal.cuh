@@ -173,6 +173,7 @@ struct Cache {
     void **vptrs_dev = nullptr;
     std::vector<CUtensorMap> maps_host;
     CUtensorMap *maps_dev = nullptr; // [n_layers][2] with the verify tile's box, then [n_layers][2] with the prefill tile's
+    std::vector<std::pair<void *, size_t>> guarded; // the checked build: buffers bracketed by canary bytes (pointer, size)
     float *qr = nullptr;             // [4][16][256] normalised and rotated queries of mkv_attn_step (stream-ordered)
     float *part_ml = nullptr;        // split-K scratch, shared by the layers (stream-ordered), grow-only
     float *part_o = nullptr;

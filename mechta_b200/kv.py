@@ -246,10 +246,20 @@ class KvCache:
             raise MkvError(_lib.ERR_FORMAT, "root of another format or layer count")
         check(_lib.lib().mkv_restore(self._h, root.p, root.payload.data_ptr(), root.payload.numel()))
 
+    def check_guards(self) -> int:
+        """Canary bytes around this cache's buffers that were overwritten (always 0 with the shipped library, which has no
+        guards; the checked build is `make -C mechta_b200/csrc checks`, selected with MKV_LIB_PATH)."""
+        bad = C.c_uint64(0)
+        check(_lib.lib().mkv_cache_check_guards(self._h, C.byref(bad)))
+        return int(bad.value)
+
     def close(self) -> None:
         if self._h:
+            bad = self.check_guards() if _lib.lib().mkv_checks_enabled() else 0
             _lib.lib().mkv_cache_destroy(self._h)
             self._h = C.c_void_p()
+            if bad:
+                raise _lib.MkvError(-1, f"{bad} guard bytes around the cache's buffers were overwritten")
 
     def __del__(self):
         try:
