@@ -85,6 +85,7 @@ struct VtShared {
     VtTrace trace;
 #endif
 };
+constexpr int VT_ROW_OUTSIDE = 1 << 30; // a row coordinate beyond any cache (at most 2^18 + 2^10 rows)
 static_assert(sizeof(VtShared) <= VT_MISC_BYTES, "VtShared outgrew its place in shared memory");
 
 __device__ __forceinline__ bool vt_wait(uint32_t bar, uint32_t parity, VtShared *sh, uint32_t *status) {
@@ -172,7 +173,11 @@ verify_f16_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
         const CUtensorMap *map = is_v ? vmap : kmap;
         // the two 64-key boxes of the tile are placed on their own: in a ring cache the second may wrap to row 0
         const uint32_t key0 = k_begin + tile * VT_TILE;
-        const int y0 = (int)(EXT ? cache_row(it, key0) : key0 - it.row0), y1 = EXT ? (int)cache_row(it, key0 + 64u) : y0 + 64;
+        // A second half wholly past this CTA's keys (its piece is an odd number of 64-key units long) is not fetched: its box
+        // starts at a row far outside the tensor, which TMA answers with the fill value, zero, without touching memory.
+        // Those keys are masked, and zeros keep the masked weights' 0 x V finite.
+        const int y0 = (int)(EXT ? cache_row(it, key0) : key0 - it.row0);
+        const int y1 = key0 + 64u >= k_end ? VT_ROW_OUTSIDE : EXT ? (int)cache_row(it, key0 + 64u) : y0 + 64;
         const int x = (int)(kvh * 256u);
 #pragma unroll
         for (int db = 0; db < 4; db++) {

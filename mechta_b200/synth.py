@@ -32,7 +32,7 @@ def session_lengths(seed: int, n: int, lo: int = 1024, hi: int = 131072) -> np.n
 
 def step_inputs(seed: int, ntok: int):
     """Inputs of a fused layer step: qf [ntok][16][512] (query | gate per head), kb [ntok][2][256], vb [ntok][512],
-    the two RMSNorm weights [256] (around 1) and per-head sink logits [16]."""
+    the two RMSNorm weights [256] (close to 1) and per-head sink logits [16]."""
     qf = normal(seed, S_QF, 0, (ntok, 16, 512)) * np.float32(1.5)
     kb = normal(seed, S_KNEW, 1, (ntok, 2, 256)) * np.float32(0.7)
     vb = normal(seed, S_VNEW, 1, (ntok, 512))
