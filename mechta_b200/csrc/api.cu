@@ -293,7 +293,7 @@ static mkv_status verify_common(Cache *c, int layer, uint32_t first_pos, uint32_
     if (st != MKV_OK) return st;
     if (c->ring && (st = apply_window(c, &it, 0, nullptr)) != MKV_OK) return st;
     if ((st = use_device(c->ctx)) != MKV_OK) return st;
-    plan_items(c->ctx, &it, 1, plan_quantum(c->fmt));
+    plan_items(c->ctx, &it, 1);
     Cache *cc[1] = {c};
     if ((st = place_scratch(cc, &it, 1)) != MKV_OK) return st;
     return launch_verify(c->ctx, c->fmt, &it, 1, false, &c->maps_host[2 * layer], &c->maps_host[2 * layer + 1]);
@@ -809,7 +809,7 @@ mkv_status mkv_attn_verify_window(mkv_cache *h, int layer, uint32_t window, cons
     if (st != MKV_OK) return st;
     if ((st = apply_window(c, &it, window, sinks)) != MKV_OK) return st;
     if ((st = use_device(c->ctx)) != MKV_OK) return st;
-    plan_items(c->ctx, &it, 1, plan_quantum(c->fmt));
+    plan_items(c->ctx, &it, 1);
     Cache *cc[1] = {c};
     if ((st = place_scratch(cc, &it, 1)) != MKV_OK) return st;
     return launch_verify(c->ctx, c->fmt, &it, 1, false, &c->maps_host[2 * layer], &c->maps_host[2 * layer + 1]);
@@ -861,7 +861,7 @@ mkv_status mkv_attn_step(mkv_cache *h, int layer, uint32_t first_pos, uint32_t p
     if (st == MKV_OK) st = use_device(c->ctx);
     Cache *cc[1] = {c};
     if (st == MKV_OK) {
-        plan_items(c->ctx, &it, 1, plan_quantum(c->fmt));
+        plan_items(c->ctx, &it, 1);
         st = place_scratch(cc, &it, 1);
     }
     it.out = ag;
@@ -1005,7 +1005,7 @@ mkv_status mkv_attn_verify_exchange(mkv_cache *hc, mkv_exchange *hx, int layer, 
     mkv_status st = fill_item(c, layer, first_pos, pos, ntok, q, out, true, &it);
     if (st != MKV_OK) return st;
     if ((st = use_device(c->ctx)) != MKV_OK) return st;
-    plan_items(c->ctx, &it, 1, plan_quantum(c->fmt));
+    plan_items(c->ctx, &it, 1);
     Cache *cc[1] = {c};
     if ((st = place_scratch(cc, &it, 1)) != MKV_OK) return st;
     const uint32_t epoch = ++ex->epoch; // every rank makes the same calls, so the call number agrees everywhere
@@ -1043,7 +1043,7 @@ mkv_status mkv_attn_verify_batch(mkv_ctx *h, const mkv_verify_item *items, int n
     }
     mkv_status st = use_device(ctx);
     if (st != MKV_OK) return st;
-    plan_items(ctx, its.data(), n, plan_quantum(fmt));
+    plan_items(ctx, its.data(), n);
     if ((st = place_scratch(caches.data(), its.data(), n)) != MKV_OK) return st;
     return launch_verify(ctx, fmt, its.data(), n, true, nullptr, nullptr);
 }
@@ -1115,7 +1115,7 @@ mkv_status mkv_attn_prefill(mkv_cache *h, int layer, uint32_t first_pos, uint32_
             st = fill_item(c, layer, first_pos, pos0 + t, nt, q + (size_t)t * 4096, out + (size_t)t * 4096, false, &its[g]);
             if (st != MKV_OK) return st;
         }
-        plan_items(c->ctx, its.data(), groups, plan_quantum(c->fmt));
+        plan_items(c->ctx, its.data(), groups);
         if ((st = place_scratch(caches.data(), its.data(), groups)) != MKV_OK) return st;
         if ((st = launch_verify(c->ctx, c->fmt, its.data(), groups, true, nullptr, nullptr)) != MKV_OK) return st;
         done += 4u * groups;

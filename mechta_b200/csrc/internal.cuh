@@ -209,8 +209,6 @@ mkv_status launch_step_prep(Ctx *ctx, mkv_fmt fmt, const float *qf, const float 
 // a shard without any visible key: its (empty) record rows still go to every rank, and the ranks' rows are merged into `out`
 mkv_status launch_exchange_empty(Ctx *ctx, const PushInfo *push, uint32_t epoch, uint32_t ntok, float *out);
 // plans the split of the items so that the grid fills the SMs once
-void plan_items(Ctx *ctx, VerifyItem *items, int n, uint32_t quantum = 1);
-// the quantum of plan_items for a cache format
-inline uint32_t plan_quantum(mkv_fmt fmt) { return fmt == MKV_F32 ? 4u : 1u; }
+void plan_items(Ctx *ctx, VerifyItem *items, int n);
 
 } // namespace mkv

@@ -774,10 +774,9 @@ extern "C" mkv_status mkv_static_status(int device, void *stream, uint32_t *stat
 namespace mkv {
 
 // Chooses tiles_per_split so that all items together fill the SMs in one wave (one CTA per SM), and lays
-// the items out in the flattened grid. Items must have tile_begin / tile_end set. `quantum`: tiles_per_split is
-// a multiple of it (the f32 kernel works in tiles of four 32-key units; a piece that is a whole number of them
-// loads no keys of its neighbour).
-void plan_items(Ctx *ctx, VerifyItem *items, int n, uint32_t quantum) {
+// the items out in the flattened grid. Items must have tile_begin / tile_end set. (A piece need not be a whole number
+// of the kernels' tiles: they do not fetch the part of a last tile that lies past the piece.)
+void plan_items(Ctx *ctx, VerifyItem *items, int n) {
     uint64_t tiles = 0;
     uint32_t min_tps = 1;
     for (int i = 0; i < n; i++) {
@@ -789,8 +788,7 @@ void plan_items(Ctx *ctx, VerifyItem *items, int n, uint32_t quantum) {
     const uint32_t budget = (uint32_t)ctx->sm_count;
     uint32_t tps = (uint32_t)((tiles + budget - 1) / budget);
     if (tps < min_tps) tps = min_tps;
-    tps = (tps + quantum - 1) / quantum * quantum;
-    for (;; tps += quantum) {
+    for (;; tps++) {
         uint64_t ctas = 0;
         for (int i = 0; i < n; i++) ctas += 2ull * ((items[i].tile_end - items[i].tile_begin + tps - 1) / tps);
         if (ctas <= budget || ctas <= 2ull * (uint64_t)n) break; // one wave, or nothing left to merge

@@ -71,6 +71,7 @@ constexpr uint32_t FT_NBAR = 3 * FT_NSLOT + 7;
 constexpr uint32_t FT_OFF_MISC = FT_OFF_BAR + FT_NBAR * 8;
 constexpr uint32_t FT_SMEM = FT_OFF_MISC + 64 + 1024;
 constexpr uint32_t FT_COL_S = 0, FT_COL_O = 128, FT_COLS = 512; // S^T: 2 x 64 columns; O_t^T: 4 blocks x 64 columns
+constexpr int FT_ROW_OUTSIDE = 1 << 30; // a row coordinate beyond any cache (at most 2^18 + 2^10 rows)
 constexpr long long FT_WAIT_LIMIT = 2000000000ll;
 constexpr float FT_LOG2E = 1.4426950408889634f;
 constexpr float FT_C2 = SCALE * FT_LOG2E;
@@ -87,11 +88,13 @@ struct FtShared {
 // Measurement build only: cycles each role spent waiting, summed over the CTAs of all launches since the last read.
 #ifdef MKV_MEASURE
 enum { FP_CTAS, FP_TOTAL, FP_PDL, FP_PROD_EMPTY, FP_MMA_IDLE, FP_MMA_Q, FP_CONV_FULL, FP_SM_S, FP_SM_O, FP_SM_PDL, FP_FIRST_S,
-       FP_MERGE, FP_N };
-__device__ unsigned long long g_ft_probe[16];
+       FP_MERGE, FP_T_PDL, FP_T_QDONE, FP_T_LASTS, FP_T_FOLDED, FP_T_PUBLISH, FP_T_ROLES, FP_N };
+__device__ unsigned long long g_ft_probe[24];
 #define FT_PROBE_BEGIN(cond) long long fp_t0 = 0; if (cond) fp_t0 = clock64()
 #define FT_PROBE_END(cond, which) do { if (cond) atomicAdd(&g_ft_probe[which], (unsigned long long)(clock64() - fp_t0)); } while (0)
+#define FT_STAMP(cond, which) do { if (cond) atomicAdd(&g_ft_probe[which], (unsigned long long)(clock64() - fp_start)); } while (0)
 #else
+#define FT_STAMP(cond, which) do { } while (0)
 #define FT_PROBE_BEGIN(cond) do { } while (0)
 #define FT_PROBE_END(cond, which) do { } while (0)
 #endif
@@ -243,7 +246,10 @@ verify_f32_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
                 mbar_expect_tx(bar, FT_SLOT);
 #pragma unroll
                 for (int kb = 0; kb < 4; kb++) { // four boxes of 32 keys; in a ring cache each may wrap on its own
-                    const int y = (int)(EXT ? cache_row(it, key0 + 32u * kb) : key0 + 32u * kb - it.row0);
+                    // boxes wholly past this CTA's keys (a piece need not be a whole number of tiles) are not fetched: a row
+                    // far outside the tensor makes TMA fill them with zeros without touching memory; the keys are masked
+                    const uint32_t kk = key0 + 32u * kb;
+                    const int y = kk >= k_end ? FT_ROW_OUTSIDE : (int)(EXT ? cache_row(it, kk) : kk - it.row0);
                     tma_load_2d(dst + kb * FT_BOX, map, x, y, bar);
                     tma_load_2d(dst + FT_BLK + kb * FT_BOX, map, x + 32, y, bar);
                 }
@@ -379,10 +385,17 @@ verify_f32_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
         // ---------------- softmax: one thread per key of the tile (TMEM lane); owners of O ----------------
         const uint32_t w4 = warp & 3u; // the warp's TMEM lane group
         const uint32_t klane = 32u * w4 + lane, lane_addr = (32u * w4) << 16;
+        // Q of this KV head towards L2 while the kernel waits for its predecessor: 8 KB per token, two 128-byte lines per thread
+#pragma unroll
+        for (uint32_t i = 0; i < 2u; i++) {
+            const uint32_t line = (tid - FT_SOFTMAX_TID0) + 128u * i; // 64 lines per token
+            if (line < 64u * it.ntok) prefetch_l2(it.q + (size_t)(line >> 6) * 4096u + (size_t)kvh * 2048u + (size_t)(line & 63u) * 32u);
+        }
         {
             FT_PROBE_BEGIN(tid == FT_SOFTMAX_TID0);
             pdl_wait(); // Q and every global write come after this
             FT_PROBE_END(tid == FT_SOFTMAX_TID0, FP_SM_PDL);
+            FT_STAMP(tid == FT_SOFTMAX_TID0, FP_T_PDL);
         }
         // Q of this KV head to shared memory as f16 hi (rows 0-31) and lo (rows 32-63), the B operands of S^T:
         // row = tok * 8 + head % 8 (the order of q_dmx, M/dmx.rs:128-138), rows of tokens >= ntok zero; per 64-dim block
@@ -413,6 +426,7 @@ verify_f32_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
             }
             fence_proxy_async();
             mbar_arrive(bar_q_full);
+            FT_STAMP(tid == FT_SOFTMAX_TID0, FP_T_QDONE);
         }
         // token t of the step sees lowest_key(t) <= key < min(pos + 1 + t, end of the shard, end of this piece)
         const uint32_t klo = max(it.first_pos, it.key_lo);
@@ -479,6 +493,7 @@ verify_f32_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
             FT_PROBE_END(tid == FT_SOFTMAX_TID0, FP_SM_S);
 #ifdef MKV_MEASURE
             if (tid == FT_SOFTMAX_TID0 && j == 0u) atomicAdd(&g_ft_probe[FP_FIRST_S], (unsigned long long)(clock64() - fp_start));
+            FT_STAMP(tid == FT_SOFTMAX_TID0 && j + 1u == nt, FP_T_LASTS);
 #endif
             tc_fence_after();
             float t[32];
@@ -605,6 +620,7 @@ verify_f32_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
                 ok = fold(folded);
                 folded++;
             }
+            FT_STAMP(tid == FT_SOFTMAX_TID0, FP_T_FOLDED);
             const size_t piece = (size_t)kvh * it.nsplit + split;
             float *red = red_base + 128u * (red_turn & 1u);
             red[lane * 4u + w4] = ft_transpose_reduce<false>(lpart, lane);
@@ -624,6 +640,7 @@ verify_f32_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
         // the piece is published by the threads that wrote it, before the CTA's teardown (see verify_tc.cu)
         ft_bar_sync();
         if (tid == FT_SOFTMAX_TID0) sh->ticket = publish_piece(it);
+        FT_STAMP(tid == FT_SOFTMAX_TID0, FP_T_PUBLISH);
         // The other warpgroups take their registers back (for the code all warps share) only behind this barrier: a warp
         // that asked earlier, e.g. an idle one at once, could take what the softmax warp of its scheduler still waits for
         // at the top of this branch, and that warp would wait for ever.
@@ -646,6 +663,7 @@ verify_f32_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
     // this CTA's share of the merge, if its ticket gives it one (scratch in the ring, which is drained by now)
 #ifdef MKV_MEASURE
     const long long fp_merge = clock64();
+    FT_STAMP(tid == 0, FP_T_ROLES);
 #endif
     finish_item<FT_THREADS, EXT>(it, *reinterpret_cast<FinishSmem *>(smem), status, sh->ticket);
 #ifdef MKV_MEASURE
@@ -659,10 +677,10 @@ verify_f32_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
 }
 
 #ifdef MKV_MEASURE
-// Measurement build only: copies the 16 role counters of verify_f32_tc_kernel to `out16` and clears them.
-extern "C" int mkv_measure_f32_roles(unsigned long long *out16) {
-    if (cudaMemcpyFromSymbol(out16, g_ft_probe, sizeof g_ft_probe) != cudaSuccess) return 1;
-    const unsigned long long zero[16] = {};
+// Measurement build only: copies the 24 role counters of verify_f32_tc_kernel to `out24` and clears them.
+extern "C" int mkv_measure_f32_roles(unsigned long long *out24) {
+    if (cudaMemcpyFromSymbol(out24, g_ft_probe, sizeof g_ft_probe) != cudaSuccess) return 1;
+    const unsigned long long zero[24] = {};
     return cudaMemcpyToSymbol(g_ft_probe, zero, sizeof zero) != cudaSuccess;
 }
 #endif
