@@ -519,7 +519,7 @@ def run_other(args, workload):
                     "warmup": args.warmup, "ms_per_step": r.get("ms_per_step"), "higher_is_better": True, "scaling": scaling,
                     "vs_baseline": None, "dtype": dtype, "data": "synthetic", "config": {"workload": r["workload"]},
                     "roofline": {"bound": r.get("bound", "hbm"), "kernel": r.get("kernel"), "achieved": r["value"] / (world if "frac_per_gpu" in r else 1),
-                                 "peak": r.get("peak"), "peak_kind": r.get("peak_kind"), "unit": r["unit"], "frac": frac, "traffic": None},
+                                 "peak": r.get("peak"), "peak_kind": r.get("peak_kind"), "unit": r["unit"], "frac": frac, "traffic": r.get("traffic")},
                     "gpu_launches": r.get("gpu_launches", r.get("gpu_launches_per_region")), "detail": r}
             if "e2e" in r:
                 line["e2e"] = r["e2e"]

@@ -73,6 +73,11 @@ def _barrier(torch, world):
 
 # ---------------------------------------------------------------------------------------------------------------------
 
+# dram read + write per launch of verify_f32_tc_kernel at 262,076 tokens, from one ncu capture of this workload
+# (1.0744 GB read + 6.5 MB written against 1.0735 GB algorithmic); a constant, not re-measured by the bench
+NCU_TRAFFIC_BYTES_VERIFY262K_F32 = 1_080_900_000
+
+
 def measure_verify262k(ctx, stream, fmt, layers=2, steps=12, warmup=3):
     """The decode attention launch alone at 262,144 tokens: `layers` layers back to back per step, appends in between."""
     import torch
@@ -113,6 +118,7 @@ def measure_verify262k(ctx, stream, fmt, layers=2, steps=12, warmup=3):
     return {"workload": f"verify262k_{fmt.name.lower()}", "context_tokens": n, "layers": layers, "steps": steps,
             "us_per_launch": 1e3 * ms / (steps * layers), "value": gbs, "unit": "GB/s", "frac": gbs / hbm, "peak": hbm,
             "peak_kind": kind, "kernel": "verify_f16_tc_kernel" if fmt == kv.KvFormat.F16 else "verify_f32_tc_kernel",
+            "traffic": None if fmt == kv.KvFormat.F16 else NCU_TRAFFIC_BYTES_VERIFY262K_F32,
             "note": "whole loop: one append launch per step + the attention launches, inputs resident"}
 
 
