@@ -21,21 +21,23 @@ append_kernel(void *const *__restrict__ kbufs, void *const *__restrict__ vbufs, 
     // tiles below `pos` meanwhile; this kernel touches nothing before the kernel in front has finished (its inputs
     // may come from it, and the rows it overwrites after a rollback may still be read by the attention in front).
     ptx::pdl_launch_dependents();
-    ptx::pdl_wait();
     // one thread = 8 consecutive elements; per (layer, token): 64 groups of K then 64 groups of V
     const size_t gid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t total = (size_t)n_layers * ntok * 128u;
-    if (gid >= total) return;
+    const bool in_range = gid < total;
     const uint32_t g = (uint32_t)(gid & 63u);
     const uint32_t is_v = (uint32_t)((gid >> 6) & 1u);
+    const uint32_t tok = in_range ? (uint32_t)((gid >> 7) % ntok) : 0u;
+    const uint32_t layer = in_range ? (uint32_t)((gid >> 7) / ntok) : 0u;
+    const uint32_t e0 = g * 8u; // element inside the position: kvh * 256 + d
+    const float *src = (is_v ? v : k) + layer * layer_stride + (size_t)tok * ROW;
+    if (in_range && (g & 3u) == 0u && (which & (is_v ? 2u : 1u))) ptx::prefetch_l2(src + e0); // the new rows towards L2 while waiting (one line per four threads)
+    ptx::pdl_wait();
+    if (!in_range) return;
     if (!(which & (is_v ? 2u : 1u))) return; // bit 0: write K, bit 1: write V
-    const uint32_t tok = (uint32_t)((gid >> 7) % ntok);
-    const uint32_t layer = (uint32_t)((gid >> 7) / ntok);
     const uint32_t gpos = pos + tok;
     if (!ring && (gpos < row_first || gpos - row_first >= capacity)) return; // row belongs to another shard
     const size_t row = ring ? gpos % ring : gpos - row_first; // ring cache: row = position % ring (W/flint_attn.wgsl:3)
-    const uint32_t e0 = g * 8u; // element inside the position: kvh * 256 + d
-    const float *src = (is_v ? v : k) + layer * layer_stride + (size_t)tok * ROW;
     float x[8];
     {
         const float4 a0 = *reinterpret_cast<const float4 *>(src + e0);
