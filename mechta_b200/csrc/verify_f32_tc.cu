@@ -237,6 +237,11 @@ verify_f32_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
                     FT_PROBE_END(true, FP_PDL);
                     waited = true;
                 }
+                // a slot comes back through the MMAs, which need the queries: the same rule for the first bounded wait here
+                if (n >= (uint32_t)FT_NSLOT && !waited) {
+                    pdl_wait();
+                    waited = true;
+                }
                 FT_PROBE_BEGIN(true);
                 if (n >= (uint32_t)FT_NSLOT && !ft_wait(bar_empty + 8u * slot, ((n / FT_NSLOT) - 1u) & 1u, sh, status)) break;
                 FT_PROBE_END(true, FP_PROD_EMPTY);
@@ -262,6 +267,9 @@ verify_f32_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
             constexpr uint32_t IDESC_QK32 = tc_idesc_f16(128, 32, false, false);
             constexpr uint32_t IDESC_PV = tc_idesc_f16(128, 64, false, true);
             const uint32_t qb = smem_base + FT_OFF_Q, pb = smem_base + FT_OFF_P;
+            // No bounded wait may start before the launch in front has finished, however long that takes: the queries come
+            // after it, and everything below waits for them in the end.
+            pdl_wait();
             FT_PROBE_BEGIN(true);
             bool ok = ft_wait(bar_q_full, 0, sh, status);
             FT_PROBE_END(true, FP_MMA_Q);
@@ -351,6 +359,8 @@ verify_f32_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
         for (uint32_t n = 0; n < nsub; n++) {
             if (((n % FT_NSLOT) & 1u) != c) continue; // slots 0, 2, 4 -> the first four warps, 1, 3 -> the other four
             const uint32_t slot = n % FT_NSLOT;
+            // the sub-tiles beyond the first ring-full are loaded once slots come back, i.e. after the queries: as above
+            if (n >= (uint32_t)FT_NSLOT && n < 2u * FT_NSLOT) pdl_wait();
             FT_PROBE_BEGIN(tid == 128u);
             if (!__all_sync(0xffffffffu, ft_wait(bar_full + 8u * slot, (n / FT_NSLOT) & 1u, sh, status))) break;
             FT_PROBE_END(tid == 128u, FP_CONV_FULL);
