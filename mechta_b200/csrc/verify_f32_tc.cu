@@ -348,6 +348,7 @@ verify_f32_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
             }
         }
       }
+      __syncwarp(); // the lanes that had no role wait here for the one that had: the barrier below wants whole warps
       ft_bar_roles(); // registers come back only after the softmax warps have returned theirs (see there)
       asm volatile("setmaxnreg.inc.sync.aligned.u32 128;");
     } else if (warp < 12) {
@@ -388,6 +389,7 @@ verify_f32_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_conv + 8u * slot);
         }
+        __syncwarp();
         ft_bar_roles();
         asm volatile("setmaxnreg.inc.sync.aligned.u32 128;");
     } else {
