@@ -36,6 +36,23 @@ __device__ __forceinline__ const VerifyItem &pick_item(const VerifyItem *items, 
     return items[lo];
 }
 
+// The same with the launch's parameter block: one item and its tensor maps, or a few items (maps in device memory).
+__device__ __forceinline__ const VerifyItem &pick_item(const VerifyItem *items, int n_items, const VerifyLaunch &single, uint32_t cta) {
+    return pick_item(items, n_items, single.item, cta);
+}
+__device__ __forceinline__ const VerifyItem &pick_item(const VerifyItem *, int n_items, const VerifyLaunchBatch &few, uint32_t cta) {
+    int lo = 0;
+    for (int i = 1; i < n_items; i++)
+        if (cta >= few.items[i].cta_begin) lo = i;
+    return few.items[lo];
+}
+__device__ __forceinline__ const CUtensorMap *launch_map(const VerifyItem *items, const VerifyItem &it, const VerifyLaunch &single, bool v) {
+    return items ? (v ? it.vmap : it.kmap) : (v ? &single.vmap : &single.kmap);
+}
+__device__ __forceinline__ const CUtensorMap *launch_map(const VerifyItem *, const VerifyItem &it, const VerifyLaunchBatch &, bool v) {
+    return v ? it.vmap : it.kmap;
+}
+
 constexpr int FIN_MAX_THREADS = 512;
 constexpr long long FIN_WAIT_LIMIT = 4000000000ll; // about two seconds of SM clocks
 constexpr uint32_t FIN_JOBS = 64;                  // one job per row (kvh * 32 + row) of the item

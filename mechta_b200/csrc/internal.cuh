@@ -107,6 +107,13 @@ struct VerifyLaunch {
     alignas(64) CUtensorMap vmap;
 };
 
+// A batch of a few items carried in the kernel's parameter space (their tensor maps stay in device memory): no staging
+// copy stands between two launches, so the launches of a step's layers keep their programmatic overlap.
+constexpr int PARAM_ITEMS = 8;
+struct VerifyLaunchBatch {
+    VerifyItem items[PARAM_ITEMS];
+};
+
 struct Ctx;
 struct Cache;
 

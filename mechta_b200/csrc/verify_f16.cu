@@ -471,6 +471,8 @@ mkv_status verify_tc_setup_device();
 mkv_status launch_verify_f32_tc(Ctx *ctx, const VerifyItem *items_dev, int n, const VerifyLaunch &single, uint32_t total_ctas,
                                 bool ext);
 mkv_status verify_f32_tc_setup_device();
+mkv_status launch_verify_f16_tc_few(Ctx *ctx, const VerifyLaunchBatch &few, int n, uint32_t total_ctas, bool ext);
+mkv_status launch_verify_f32_tc_few(Ctx *ctx, const VerifyLaunchBatch &few, int n, uint32_t total_ctas, bool ext);
 
 // MKV_VERIFY=mma selects the warp-MMA kernel of this file for the f16 cache; the default is the tcgen05 kernel.
 static bool verify_use_tc() {
@@ -518,8 +520,13 @@ mkv_status launch_verify(Ctx *ctx, mkv_fmt fmt, VerifyItem *items_host, int n, b
         items_host[i].counter = ctx->counters_dev + i;
         items_host[i].ticket_base = ctx->counter_base[i];
     }
+    // A batch of a few items travels in the kernel's parameter space: no staging copy between two launches (a copy in
+    // the stream ends the programmatic overlap of the launches either side of it). Larger batches, and the rare batch with
+    // an item that sees no key (its empty result comes from the small merge kernel, which reads the staged items), are staged.
+    const bool tc = fmt == MKV_F16 ? verify_use_tc() : verify32_use_tc();
+    const bool few = batch && tc && n <= PARAM_ITEMS && !any_empty && total > 0;
     const VerifyItem *items_dev = nullptr;
-    if (batch) {
+    if (batch && !few) {
         // next staging slot; wait for the copy that last used it
         const int slot = ctx->slot_next;
         ctx->slot_next = (slot + 1) % Ctx::SLOTS;
@@ -554,7 +561,14 @@ mkv_status launch_verify(Ctx *ctx, mkv_fmt fmt, VerifyItem *items_host, int n, b
         ctx->prof_used++;
         MKV_CUDA(cudaEventRecord(e0, ctx->stream));
     }
-    if (total > 0) {
+    if (few) {
+        VerifyLaunchBatch pb;
+        memset(&pb, 0, sizeof pb);
+        memcpy(pb.items, items_host, sizeof(VerifyItem) * (size_t)n);
+        mkv_status st = fmt == MKV_F16 ? launch_verify_f16_tc_few(ctx, pb, n, total, ext) : launch_verify_f32_tc_few(ctx, pb, n, total, ext);
+        if (st != MKV_OK) return st;
+        for (int i = 0; i < n; i++) ctx->counter_base[i] += 2u * items_host[i].nsplit;
+    } else if (total > 0) {
         if (fmt == MKV_F16 && verify_use_tc()) {
             mkv_status st = launch_verify_f16_tc(ctx, items_dev, n, single, total, ext);
             if (st != MKV_OK) return st;

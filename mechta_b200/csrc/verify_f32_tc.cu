@@ -154,15 +154,15 @@ __device__ __forceinline__ void ft_split8(const float4 &a, const float4 &b, uint
     lo = make_uint4(l[0], l[1], l[2], l[3]);
 }
 
-template <bool EXT>
+template <bool EXT, typename Launch>
 __global__ void __launch_bounds__(FT_THREADS, 1)
-verify_f32_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __grid_constant__ VerifyLaunch single,
+verify_f32_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __grid_constant__ Launch single,
                      uint32_t *__restrict__ status) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *smem = smem_raw + (smem_base - smem_u32(smem_raw));
 
-    const VerifyItem &it = pick_item(items, n_items, single.item, blockIdx.x);
+    const VerifyItem &it = pick_item(items, n_items, single, blockIdx.x);
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const uint32_t local = blockIdx.x - it.cta_begin;
     if (local >= 2u * it.nsplit) return;
@@ -176,7 +176,7 @@ verify_f32_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
     const uint32_t k_begin = t0 * TILE32, k_end = t1 * TILE32;
     const uint32_t nt = (k_end - k_begin + FT_TILE - 1u) / FT_TILE;
     const uint32_t nsub = 8u * nt; // four sub-tiles per K tile and per V tile
-    const CUtensorMap *kmap = items ? it.kmap : &single.kmap, *vmap = items ? it.vmap : &single.vmap;
+    const CUtensorMap *kmap = launch_map(items, it, single, false), *vmap = launch_map(items, it, single, true);
     const uint32_t bar0 = smem_base + FT_OFF_BAR;
     const uint32_t bar_full = bar0, bar_conv = bar_full + 8u * FT_NSLOT, bar_empty = bar_conv + 8u * FT_NSLOT;
     const uint32_t bar_s_full = bar_empty + 8u * FT_NSLOT, bar_p_full = bar_s_full + 16u, bar_o_full = bar_p_full + 16u;
@@ -698,13 +698,15 @@ extern "C" int mkv_measure_f32_roles(unsigned long long *out24) {
 #endif
 
 mkv_status verify_f32_tc_setup_device() {
-    MKV_CUDA(cudaFuncSetAttribute(verify_f32_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FT_SMEM));
-    MKV_CUDA(cudaFuncSetAttribute(verify_f32_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FT_SMEM));
+    MKV_CUDA(cudaFuncSetAttribute(verify_f32_tc_kernel<false, VerifyLaunch>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FT_SMEM));
+    MKV_CUDA(cudaFuncSetAttribute(verify_f32_tc_kernel<true, VerifyLaunch>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FT_SMEM));
+    MKV_CUDA(cudaFuncSetAttribute(verify_f32_tc_kernel<false, VerifyLaunchBatch>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FT_SMEM));
+    MKV_CUDA(cudaFuncSetAttribute(verify_f32_tc_kernel<true, VerifyLaunchBatch>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FT_SMEM));
     return MKV_OK;
 }
 
-mkv_status launch_verify_f32_tc(Ctx *ctx, const VerifyItem *items_dev, int n, const VerifyLaunch &single, uint32_t total_ctas,
-                                bool ext) {
+template <typename Launch>
+static mkv_status launch_verify_f32_tc_any(Ctx *ctx, const VerifyItem *items_dev, int n, const Launch &single, uint32_t total_ctas, bool ext) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(total_ctas);
     cfg.blockDim = dim3(FT_THREADS);
@@ -715,10 +717,19 @@ mkv_status launch_verify_f32_tc(Ctx *ctx, const VerifyItem *items_dev, int n, co
     at[0].val.programmaticStreamSerializationAllowed = ctx->pdl ? 1 : 0;
     cfg.attrs = at;
     cfg.numAttrs = 1;
-    if (ext) MKV_CUDA(cudaLaunchKernelEx(&cfg, verify_f32_tc_kernel<true>, items_dev, n, single, ctx->dev_status));
-    else MKV_CUDA(cudaLaunchKernelEx(&cfg, verify_f32_tc_kernel<false>, items_dev, n, single, ctx->dev_status));
+    if (ext) MKV_CUDA(cudaLaunchKernelEx(&cfg, verify_f32_tc_kernel<true, Launch>, items_dev, n, single, ctx->dev_status));
+    else MKV_CUDA(cudaLaunchKernelEx(&cfg, verify_f32_tc_kernel<false, Launch>, items_dev, n, single, ctx->dev_status));
     ctx->launches++;
     return MKV_OK;
+}
+
+mkv_status launch_verify_f32_tc(Ctx *ctx, const VerifyItem *items_dev, int n, const VerifyLaunch &single, uint32_t total_ctas, bool ext) {
+    return launch_verify_f32_tc_any(ctx, items_dev, n, single, total_ctas, ext);
+}
+
+// a few items in the parameter space (see VerifyLaunchBatch)
+mkv_status launch_verify_f32_tc_few(Ctx *ctx, const VerifyLaunchBatch &few, int n, uint32_t total_ctas, bool ext) {
+    return launch_verify_f32_tc_any(ctx, static_cast<const VerifyItem *>(nullptr), n, few, total_ctas, ext);
 }
 
 } // namespace mkv

@@ -129,15 +129,15 @@ __device__ __forceinline__ float vt_transpose_reduce(float (&v)[32], uint32_t la
 
 // EXT: ring rows, sliding window and sinks (mkv_attn_verify_window, ring caches); the plain path is instantiated
 // without them, which keeps a division and some branches out of the producer's refill path.
-template <bool EXT>
+template <bool EXT, typename Launch>
 __global__ void __launch_bounds__(256, 1)
-verify_f16_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __grid_constant__ VerifyLaunch single,
+verify_f16_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __grid_constant__ Launch single,
                      uint32_t *__restrict__ status) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *smem = smem_raw + (smem_base - smem_u32(smem_raw));
 
-    const VerifyItem &it = pick_item(items, n_items, single.item, blockIdx.x);
+    const VerifyItem &it = pick_item(items, n_items, single, blockIdx.x);
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const uint32_t local = blockIdx.x - it.cta_begin;
     if (local >= 2u * it.nsplit) return;
@@ -149,7 +149,7 @@ verify_f16_tc_kernel(const VerifyItem *__restrict__ items, int n_items, const __
     const uint32_t t1 = min(t0 + it.tiles_per_split, it.tile_end);
     const uint32_t k_begin = t0 * TILE, k_end = t1 * TILE;          // this CTA's keys
     const uint32_t nt = ph == 3u ? 0u : (k_end - k_begin + VT_TILE - 1u) / VT_TILE;
-    const CUtensorMap *kmap = items ? it.kmap : &single.kmap, *vmap = items ? it.vmap : &single.vmap;
+    const CUtensorMap *kmap = launch_map(items, it, single, false), *vmap = launch_map(items, it, single, true);
     const uint32_t bar0 = smem_base + VT_OFF_BAR;
     const uint32_t bar_full = bar0, bar_empty = bar0 + 8u * VT_NSLOT, bar_s_full = bar0 + 16u * VT_NSLOT;
     const uint32_t bar_p_full = bar_s_full + 16u, bar_pv_done = bar_p_full + 16u;
@@ -606,13 +606,15 @@ extern "C" int mkv_trace_read(void *dst, int max_records) {
 #endif
 
 mkv_status verify_tc_setup_device() {
-    MKV_CUDA(cudaFuncSetAttribute(verify_f16_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)VT_SMEM));
-    MKV_CUDA(cudaFuncSetAttribute(verify_f16_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)VT_SMEM));
+    MKV_CUDA(cudaFuncSetAttribute(verify_f16_tc_kernel<false, VerifyLaunch>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)VT_SMEM));
+    MKV_CUDA(cudaFuncSetAttribute(verify_f16_tc_kernel<true, VerifyLaunch>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)VT_SMEM));
+    MKV_CUDA(cudaFuncSetAttribute(verify_f16_tc_kernel<false, VerifyLaunchBatch>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)VT_SMEM));
+    MKV_CUDA(cudaFuncSetAttribute(verify_f16_tc_kernel<true, VerifyLaunchBatch>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)VT_SMEM));
     return MKV_OK;
 }
 
-mkv_status launch_verify_f16_tc(Ctx *ctx, const VerifyItem *items_dev, int n, const VerifyLaunch &single, uint32_t total_ctas,
-                                bool ext) {
+template <typename Launch>
+static mkv_status launch_verify_f16_tc_any(Ctx *ctx, const VerifyItem *items_dev, int n, const Launch &single, uint32_t total_ctas, bool ext) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(total_ctas);
     cfg.blockDim = dim3(256);
@@ -623,10 +625,19 @@ mkv_status launch_verify_f16_tc(Ctx *ctx, const VerifyItem *items_dev, int n, co
     at[0].val.programmaticStreamSerializationAllowed = ctx->pdl ? 1 : 0;
     cfg.attrs = at;
     cfg.numAttrs = 1;
-    if (ext) MKV_CUDA(cudaLaunchKernelEx(&cfg, verify_f16_tc_kernel<true>, items_dev, n, single, ctx->dev_status));
-    else MKV_CUDA(cudaLaunchKernelEx(&cfg, verify_f16_tc_kernel<false>, items_dev, n, single, ctx->dev_status));
+    if (ext) MKV_CUDA(cudaLaunchKernelEx(&cfg, verify_f16_tc_kernel<true, Launch>, items_dev, n, single, ctx->dev_status));
+    else MKV_CUDA(cudaLaunchKernelEx(&cfg, verify_f16_tc_kernel<false, Launch>, items_dev, n, single, ctx->dev_status));
     ctx->launches++;
     return MKV_OK;
+}
+
+mkv_status launch_verify_f16_tc(Ctx *ctx, const VerifyItem *items_dev, int n, const VerifyLaunch &single, uint32_t total_ctas, bool ext) {
+    return launch_verify_f16_tc_any(ctx, items_dev, n, single, total_ctas, ext);
+}
+
+// a few items in the parameter space (see VerifyLaunchBatch)
+mkv_status launch_verify_f16_tc_few(Ctx *ctx, const VerifyLaunchBatch &few, int n, uint32_t total_ctas, bool ext) {
+    return launch_verify_f16_tc_any(ctx, static_cast<const VerifyItem *>(nullptr), n, few, total_ctas, ext);
 }
 
 } // namespace mkv
