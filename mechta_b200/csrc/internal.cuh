@@ -109,10 +109,11 @@ struct VerifyLaunch {
 
 // A batch of a few items carried in the kernel's parameter space (their tensor maps stay in device memory): no staging
 // copy stands between two launches, so the launches of a step's layers keep their programmatic overlap.
-constexpr int PARAM_ITEMS = 8;
+constexpr int PARAM_ITEMS = 16;
 struct VerifyLaunchBatch {
     VerifyItem items[PARAM_ITEMS];
 };
+static_assert(sizeof(VerifyLaunchBatch) <= 4000, "the parameter block of a small batch must fit the 4 KB of kernel parameters");
 
 struct Ctx;
 struct Cache;
