@@ -456,7 +456,7 @@ def run_decode65k(args):
                 guarded(bw.measure_prefill, ctx, stream, 3, 1)
             else:
                 guarded(bw.measure_longctx, ctx, stream, world, rank, local, group, short, 3, args.exchange)
-                guarded(bw.measure_sessions, ctx, stream, world, rank, min(short, 10), 3)
+                guarded(bw.measure_sessions, ctx, stream, world, rank, short, 3)
 
         cpu = None
         if rank == 0 and world == 1 and not args.no_cpu_baseline:
