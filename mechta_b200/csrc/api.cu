@@ -910,8 +910,7 @@ mkv_status mkv_exchange_create(mkv_ctx *h, int rank, int world, mkv_exchange **o
     ex->ctx = ctx;
     ex->rank = rank;
     ex->world = world;
-    ex->flag_off = (2u * (size_t)world * SLOT_FLOATS * sizeof(float) + 255u) & ~(size_t)255u;
-    ex->mailbox_bytes = ex->flag_off + 2u * MAX_PEERS * FLAG_WORDS * sizeof(uint32_t);
+    ex->mailbox_bytes = 2u * (size_t)world * SLOT_WORDS * sizeof(unsigned long long);
     if (cudaMalloc(&ex->mailbox, ex->mailbox_bytes) != cudaSuccess || cudaMalloc(&ex->push_dev, sizeof(PushInfo)) != cudaSuccess) {
         cudaGetLastError();
         set_error("out of device memory for the exchange mailbox");
@@ -962,13 +961,11 @@ mkv_status mkv_exchange_connect(mkv_exchange *h, const void *handles) {
     memset(&pi, 0, sizeof pi);
     pi.world = (uint32_t)ex->world;
     for (int p = 0; p < 2; p++) {
-        pi.inbox[p] = reinterpret_cast<const float *>(ex->mailbox) + (size_t)p * ex->world * SLOT_FLOATS;
-        pi.inflag[p] = reinterpret_cast<const uint32_t *>(ex->mailbox + ex->flag_off) + (size_t)p * MAX_PEERS * FLAG_WORDS;
+        pi.inbox[p] = reinterpret_cast<const unsigned long long *>(ex->mailbox) + (size_t)p * ex->world * SLOT_WORDS;
         for (int d = 0; d < ex->world; d++) {
             unsigned char *base = static_cast<unsigned char *>(ex->peer_base[d]);
             if (!base) continue;
-            pi.slot[p][d] = reinterpret_cast<float *>(base) + ((size_t)p * ex->world + ex->rank) * SLOT_FLOATS;
-            pi.rowflag[p][d] = reinterpret_cast<uint32_t *>(base + ex->flag_off) + ((size_t)p * MAX_PEERS + ex->rank) * FLAG_WORDS;
+            pi.slot[p][d] = reinterpret_cast<unsigned long long *>(base) + ((size_t)p * ex->world + ex->rank) * SLOT_WORDS;
         }
     }
     MKV_CUDA(cudaMemcpy(ex->push_dev, &pi, sizeof pi, cudaMemcpyHostToDevice));
@@ -1008,7 +1005,8 @@ mkv_status mkv_attn_verify_exchange(mkv_cache *hc, mkv_exchange *hx, int layer, 
     plan_items(c->ctx, &it, 1);
     Cache *cc[1] = {c};
     if ((st = place_scratch(cc, &it, 1)) != MKV_OK) return st;
-    const uint32_t epoch = ++ex->epoch; // every rank makes the same calls, so the call number agrees everywhere
+    if (++ex->epoch == 0u) ++ex->epoch; // never 0: a cleared mailbox must not look like a delivery
+    const uint32_t epoch = ex->epoch;   // every rank makes the same calls, so the call number agrees everywhere
     it.push = ex->push_dev;
     it.push_world = (uint32_t)ex->world;
     it.push_epoch = epoch;

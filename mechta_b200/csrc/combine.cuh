@@ -77,44 +77,60 @@ __device__ __forceinline__ uint32_t publish_piece(const VerifyItem &it) {
     return atomicAdd(it.counter, 1u) - it.ticket_base;
 }
 
-// Row rr (= tok * 16 + head) of this rank's record has just been stored into every rank's mailbox by the threads
-// of this CTA. Raises the row's flag everywhere, waits for the same row of every other rank and merges the ranks'
-// rows into out[rr][256]. All NT threads of the CTA call this. On a wait that runs out the status word is set and
-// the output is left alone.
-template <int NT>
-__device__ __forceinline__ bool exchange_row(const PushInfo &P, uint32_t epoch, uint32_t rr, float *out, uint32_t *status) {
-    const uint32_t tid = threadIdx.x, par = epoch & 1u, world = P.world;
-    __syncthreads(); // the stores of all threads precede the releases below
-    if (tid < world && P.rowflag[par][tid]) ptx::st_release_sys(P.rowflag[par][tid] + rr, epoch);
-    bool ok = true;
-    if (tid < world) {
-        const uint32_t *f = P.inflag[par] + (size_t)tid * FLAG_WORDS + rr;
+// One value of a record as it travels: the f32 bits below the epoch.
+__device__ __forceinline__ unsigned long long exch_word(float v, uint32_t epoch) {
+    return ((unsigned long long)epoch << 32) | (unsigned long long)__float_as_uint(v);
+}
+// Polls one word of the own mailbox until it carries `epoch` (bounded); the value's bits come back in `bits`.
+__device__ __forceinline__ bool exch_poll(const unsigned long long *p, uint32_t epoch, uint32_t &bits) {
+    unsigned long long w = ptx::ld_relaxed_sys_u64(p);
+    if ((uint32_t)(w >> 32) != epoch) {
         const long long t0 = clock64();
-        while (ptx::ld_acquire_sys(f) != epoch) {
-            __nanosleep(40);
-            if (clock64() - t0 > FIN_WAIT_LIMIT) {
-                ok = false;
-                break;
-            }
-        }
+        do {
+            __nanosleep(20);
+            if (clock64() - t0 > FIN_WAIT_LIMIT) return false;
+            w = ptx::ld_relaxed_sys_u64(p);
+        } while ((uint32_t)(w >> 32) != epoch);
+    }
+    bits = (uint32_t)w;
+    return true;
+}
+
+// Row rr (= tok * 16 + head) of this rank's record has just been stored into every rank's mailbox by threads of this
+// CTA (words carrying `epoch`). Waits for the same row of every rank in the own mailbox, value by value, and merges the
+// ranks' rows into out[rr][256]. All NT threads of the CTA call this; `ml` is shared scratch of 2 * MAX_PEERS floats.
+// On a wait that runs out the status word is set and the output is left alone.
+template <int NT>
+__device__ __forceinline__ bool exchange_row(const PushInfo &P, uint32_t epoch, uint32_t rr, float *out, uint32_t *status, float *ml) {
+    const uint32_t tid = threadIdx.x, par = epoch & 1u, world = P.world;
+    const unsigned long long *in = P.inbox[par] + (size_t)rr * REC;
+    bool ok = true;
+    if (tid < 2u * world) { // (m, l) of every rank's row, for everybody
+        uint32_t bits = 0;
+        ok = exch_poll(in + (size_t)(tid >> 1) * SLOT_WORDS + (tid & 1u), epoch, bits);
+        ml[tid] = __uint_as_float(bits);
     }
     if (!__syncthreads_and(ok)) {
         if (tid == 0) atomicOr(status, DEV_ERR_WAIT_TIMEOUT);
         return false;
     }
-    const float *in = P.inbox[par] + (size_t)rr * REC;
     float M = NEG_BIG;
-    for (uint32_t g = 0; g < world; g++) M = fmaxf(M, __ldcg(in + (size_t)g * SLOT_FLOATS));
-    for (uint32_t d = tid; d < 256u; d += NT) {
-        float tot = 0.0f, acc = 0.0f;
-        for (uint32_t g = 0; g < world; g++) {
-            const float *x = in + (size_t)g * SLOT_FLOATS;
-            const float e = expf(__ldcg(x) - M);
-            tot += e * __ldcg(x + 1);
-            acc += e * __ldcg(x + 2 + d);
+    for (uint32_t g = 0; g < world; g++) M = fmaxf(M, ml[2u * g]);
+    float tot = 0.0f, acc = 0.0f;
+    if (tid < 256u) {
+        for (uint32_t g = 0; g < world && ok; g++) {
+            uint32_t bits = 0;
+            ok = exch_poll(in + (size_t)g * SLOT_WORDS + 2u + tid, epoch, bits);
+            const float e = expf(ml[2u * g] - M);
+            tot += e * ml[2u * g + 1u];
+            acc += e * __uint_as_float(bits);
         }
-        out[(size_t)rr * 256u + d] = acc / tot;
     }
+    if (!__syncthreads_and(ok)) { // (also keeps `ml` until everybody has read it)
+        if (tid == 0) atomicOr(status, DEV_ERR_WAIT_TIMEOUT);
+        return false;
+    }
+    if (tid < 256u) out[(size_t)rr * 256u + tid] = acc / tot;
     return true;
 }
 
@@ -211,11 +227,23 @@ __device__ __forceinline__ void merge_row(const VerifyItem &it, uint32_t r, Fini
         }
         const float tot = sm.tot;
         if (it.partial) {
-            const uint32_t ndst = it.push ? it.push->world : 1u; // the record goes to `out`, or to every rank's mailbox
-            for (uint32_t dd = 0; dd < ndst; dd++) { // plain peer stores over NVLink when pushing (no multicast)
-                float *base = it.push ? it.push->slot[it.push_epoch & 1u][dd] : it.out;
-                if (!base) continue; // a rank that never joined the exchange
-                float *rec = base + (size_t)(tok * 16u + head) * REC; // records are 8-byte aligned only
+            if (it.push) { // the row goes to every rank's mailbox: plain peer stores over NVLink (no multicast), one word per value
+                const PushInfo &P = *it.push;
+                for (uint32_t dd = 0; dd < P.world; dd++) {
+                    unsigned long long *rec = P.slot[it.push_epoch & 1u][dd];
+                    if (!rec) continue; // a rank that never joined the exchange
+                    rec += (size_t)(tok * 16u + head) * REC;
+                    ptx::st_relaxed_sys_u64(rec + 2 + 4 * tid, exch_word(a.x, it.push_epoch));
+                    ptx::st_relaxed_sys_u64(rec + 3 + 4 * tid, exch_word(a.y, it.push_epoch));
+                    ptx::st_relaxed_sys_u64(rec + 4 + 4 * tid, exch_word(a.z, it.push_epoch));
+                    ptx::st_relaxed_sys_u64(rec + 5 + 4 * tid, exch_word(a.w, it.push_epoch));
+                    if (tid == 0) {
+                        ptx::st_relaxed_sys_u64(rec, exch_word(M, it.push_epoch));
+                        ptx::st_relaxed_sys_u64(rec + 1, exch_word(tot, it.push_epoch));
+                    }
+                }
+            } else { // the un-normalised record itself (records are 8-byte aligned only)
+                float *rec = it.out + (size_t)(tok * 16u + head) * REC;
                 *reinterpret_cast<float2 *>(rec + 2 + 4 * tid) = make_float2(a.x, a.y);
                 *reinterpret_cast<float2 *>(rec + 4 + 4 * tid) = make_float2(a.z, a.w);
                 if (tid == 0) *reinterpret_cast<float2 *>(rec) = make_float2(M, tot);
@@ -239,7 +267,7 @@ __device__ __forceinline__ void merge_row(const VerifyItem &it, uint32_t r, Fini
             }
         }
     }
-    if (it.partial && it.push && !exchange_row<NT>(*it.push, it.push_epoch, tok * 16u + head, it.out, status)) {
+    if (it.partial && it.push && !exchange_row<NT>(*it.push, it.push_epoch, tok * 16u + head, it.out, status, sm.red)) {
         if (tid == 0) sm.ok = 0u; // a rank never delivered: the CTA's other rows would only wait as long again
         __syncthreads();
     }

@@ -35,16 +35,15 @@ void set_error(const char *fmt, ...);
         }                                                                                      \
     } while (0)
 
-// Peer exchange of shard records without a collective library: where a rank's merged record goes.
+// Peer exchange of shard records without a collective library: where a rank's merged record goes. Every f32 value of a
+// record travels as one 8-byte word, the value's bits below the number of the exchange call (the "epoch", never 0): a
+// word is stored and loaded whole, so a receiver that polls it and finds the current epoch has the value, with no flag
+// and no release / acquire round trip behind the data (the low-latency protocol of collective libraries).
 constexpr int MAX_PEERS = 8;
-constexpr size_t SLOT_FLOATS = 64 * 258; // one record [64 rows][258]
-constexpr size_t FLAG_WORDS = 64;        // one flag per row of a record
+constexpr size_t SLOT_WORDS = 64 * 258; // one record [64 rows][258], one 8-byte word per value
 struct PushInfo {
-    float *slot[2][MAX_PEERS];       // [epoch parity][destination rank]: this rank's record [64][258] in that rank's mailbox
-    uint32_t *rowflag[2][MAX_PEERS]; // [epoch parity][destination rank]: this rank's FLAG_WORDS flags there (a flag holds the
-                                     // epoch once that row of the record is complete)
-    const float *inbox[2];           // this rank's own mailbox: [epoch parity] -> records [world][64][258]
-    const uint32_t *inflag[2];       // and their flags [world][FLAG_WORDS]
+    unsigned long long *slot[2][MAX_PEERS]; // [epoch parity][destination rank]: this rank's record in that rank's mailbox
+    const unsigned long long *inbox[2];     // this rank's own mailbox: [epoch parity] -> records [world][64][258]
     uint32_t world;
 };
 
@@ -193,8 +192,8 @@ struct Cache {
 struct Exchange {
     Ctx *ctx = nullptr;
     int rank = 0, world = 1;
-    unsigned char *mailbox = nullptr; // records[2][world][SLOT_FLOATS] f32, then row flags[2][MAX_PEERS][FLAG_WORDS] u32
-    size_t flag_off = 0, mailbox_bytes = 0;
+    unsigned char *mailbox = nullptr; // records[2][world][SLOT_WORDS] of 8-byte (value, epoch) words
+    size_t mailbox_bytes = 0;
     void *peer_base[MAX_PEERS] = {};
     PushInfo *push_dev = nullptr;
     uint32_t epoch = 0;

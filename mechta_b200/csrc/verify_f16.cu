@@ -431,13 +431,14 @@ exchange_empty_kernel(const PushInfo *__restrict__ push, uint32_t epoch, float *
     pdl_launch_dependents();
     pdl_wait(); // the mailbox parity is free only once the launch before last has finished
     const PushInfo &P = *push;
+    __shared__ float ml[2 * MAX_PEERS];
     for (uint32_t dd = 0; dd < P.world; dd++) {
-        float *rec = P.slot[epoch & 1u][dd];
+        unsigned long long *rec = P.slot[epoch & 1u][dd];
         if (!rec) continue; // a rank that never joined the exchange
         rec += (size_t)rr * REC;
-        for (uint32_t i = tid; i < (uint32_t)REC; i += 256u) rec[i] = i == 0 ? NEG_BIG : 0.0f;
+        for (uint32_t i = tid; i < (uint32_t)REC; i += 256u) st_relaxed_sys_u64(rec + i, exch_word(i == 0 ? NEG_BIG : 0.0f, epoch));
     }
-    exchange_row<256>(P, epoch, rr, out, status);
+    exchange_row<256>(P, epoch, rr, out, status, ml);
 }
 
 mkv_status launch_exchange_empty(Ctx *ctx, const PushInfo *push, uint32_t epoch, uint32_t ntok, float *out) {
