@@ -145,13 +145,14 @@ mkv_status mkv_combine_shards(mkv_ctx *ctx, const float *recs_dev /*[n_shards][6
 
 /* The same exchange without a collective library and without a second kernel: the CTAs of the attention kernel that
  * merge its split-K pieces store each row of the rank's record straight into every rank's mailbox over NVLink (plain
- * peer stores, no multicast), raise that row's flag there, wait (bounded) for the same row of every other rank in
- * their own mailbox and write the merged row: one launch per layer. One process per GPU; the mailboxes are shared by
- * CUDA IPC:
+ * peer stores, no multicast; every value as one 8-byte word that also carries the call number, so a value that shows the
+ * current call number is the value: no flag and no fence behind the data), wait (bounded) for the same row of every
+ * other rank in their own mailbox and write the merged row: one launch per layer. One process per GPU; the mailboxes
+ * are shared by CUDA IPC:
  *   mkv_exchange_create on every rank -> mkv_exchange_handle (64 bytes) -> the host gathers the handles of all ranks
  *   in rank order -> mkv_exchange_connect(handles[world][64]).
  * Every rank then makes the same sequence of mkv_attn_verify_exchange calls (same layer, positions and q): the call
- * number is the epoch that flags carry. out_dev = f32 [ntok][16][256], final (merged over all shards) on every rank.
+ * number is the epoch the words carry. out_dev = f32 [ntok][16][256], final (merged over all shards) on every rank.
  * A rank whose handle is all zeroes counts as absent: nothing is sent to it, and since its rows never arrive the
  * bounded wait of the merging CTAs (about two seconds) runs out; the output is then left untouched and mkv_sync
  * reports MKV_ERR_CUDA (status word), after which the context is usable again. out_dev must be 16-byte aligned.
