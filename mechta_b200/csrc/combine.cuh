@@ -118,12 +118,22 @@ __device__ __forceinline__ bool exchange_row(const PushInfo &P, uint32_t epoch, 
     for (uint32_t g = 0; g < world; g++) M = fmaxf(M, ml[2u * g]);
     float tot = 0.0f, acc = 0.0f;
     if (tid < 256u) {
-        for (uint32_t g = 0; g < world && ok; g++) {
-            uint32_t bits = 0;
-            ok = exch_poll(in + (size_t)g * SLOT_WORDS + 2u + tid, epoch, bits);
-            const float e = expf(ml[2u * g] - M);
-            tot += e * ml[2u * g + 1u];
-            acc += e * __uint_as_float(bits);
+        // the words of all ranks are asked for at once (one round trip to L2, not one per rank); what has not arrived yet
+        // is polled afterwards. (Letting every thread fetch the (m, l) words too, to save the barrier above, was measured
+        // on 8 GPUs: 19.6 us per layer for the exchange against 10.7 - the polls of 256 threads per row get in the way.)
+        unsigned long long w[MAX_PEERS];
+#pragma unroll
+        for (uint32_t g = 0; g < (uint32_t)MAX_PEERS; g++)
+            w[g] = g < world ? ptx::ld_relaxed_sys_u64(in + (size_t)g * SLOT_WORDS + 2u + tid) : 0ull;
+#pragma unroll
+        for (uint32_t g = 0; g < (uint32_t)MAX_PEERS; g++) {
+            if (g < world && ok) {
+                uint32_t bits = (uint32_t)w[g];
+                if ((uint32_t)(w[g] >> 32) != epoch) ok = exch_poll(in + (size_t)g * SLOT_WORDS + 2u + tid, epoch, bits);
+                const float e = expf(ml[2u * g] - M);
+                tot += e * ml[2u * g + 1u];
+                acc += e * __uint_as_float(bits);
+            }
         }
     }
     if (!__syncthreads_and(ok)) { // (also keeps `ml` until everybody has read it)
