@@ -15,9 +15,9 @@ CHECKS = os.path.join(ROOT, "mechta_b200", "libmechta_kv_checks.so")
 
 
 def _env():
-    if not os.path.exists(CHECKS):
-        r = subprocess.run(["make", "-C", os.path.join(ROOT, "mechta_b200", "csrc"), "checks"], capture_output=True, text=True)
-        assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    # brings the checked library up to date with the sources (a no-op when it is)
+    r = subprocess.run(["make", "-C", os.path.join(ROOT, "mechta_b200", "csrc"), "checks"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     return dict(os.environ, MKV_LIB_PATH=CHECKS)
 
 
